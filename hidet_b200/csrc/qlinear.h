@@ -1,0 +1,30 @@
+// Internal interface between the quantized-linear entry points and the kernels behind them.
+#pragma once
+
+#include <cuda_runtime.h>
+#include <stddef.h>
+#include <stdint.h>
+
+namespace b200q {
+
+// How the small-M kernel splits a problem over CTAs, and the scratch that split needs.
+struct DecodePlan {
+    int n_tiles = 0;
+    int m_tiles = 0;
+    int splits = 1;            // CTAs along K per output tile
+    int iters_per_split = 0;   // 64-row k steps each of them takes
+    size_t counter_bytes = 0;  // head of the workspace: one arrival counter per output tile
+    size_t partial_bytes = 0;  // then [splits][M][N] fp32 partial sums (0 when splits == 1)
+};
+
+DecodePlan plan_decode(int64_t M, int64_t N, int64_t K);
+
+// True when the TMA-based [K, N] kernel can take these operands (16-byte aligned bases and rows).
+bool decode_kn_supported(const void *a, const void *wq, int64_t N, int64_t K);
+
+// c[M, N] = scale * (a[:, k_begin:k_end] x wq[k_begin:k_end, :]).  K is the row length of `a`.
+int launch_decode_kn(const void *a, const void *wq, const void *scale, void *c, int64_t M, int64_t N, int64_t K,
+                     int64_t k_begin, int64_t k_end, bool allow_split, void *workspace, size_t workspace_bytes,
+                     cudaStream_t stream);
+
+}  // namespace b200q

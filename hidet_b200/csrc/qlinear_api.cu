@@ -1,0 +1,113 @@
+// Entry points of the f16 x int8 quantized linear and the shape-agnostic kernel that serves operands
+// the TMA kernels cannot take (rows that are not 16-byte multiples, unaligned bases).
+#include "common.cuh"
+#include "qlinear.h"
+
+namespace b200q {
+namespace {
+
+constexpr int kGenericThreads = 128;
+
+// One thread per output element, fp32 accumulation over k in [k_begin, k_end), one rounding.
+// Adjacent threads take adjacent columns, so [K, N] weights are read coalesced; [N, K] weights are
+// read with a stride and rely on the caches.  Correctness net, not a tuned path.
+__global__ void __launch_bounds__(kGenericThreads) qlinear_generic_kernel(const __half *__restrict__ a,
+                                                                          const int8_t *__restrict__ wq,
+                                                                          const __half *__restrict__ scale,
+                                                                          __half *__restrict__ c, int64_t M, int64_t N,
+                                                                          int64_t K, int64_t k_begin, int64_t k_end,
+                                                                          int layout) {
+    const int64_t n = (int64_t)blockIdx.x * kGenericThreads + threadIdx.x;
+    const int64_t m = blockIdx.y;
+    if (n >= N || m >= M) return;
+    const __half *arow = a + m * K;
+    float acc = 0.0f;
+    if (layout == B200Q_LAYOUT_KN) {
+        for (int64_t k = k_begin; k < k_end; ++k) acc = fmaf(__half2float(arow[k]), (float)wq[k * N + n], acc);
+    } else {
+        const int8_t *wrow = wq + n * K;
+        for (int64_t k = k_begin; k < k_end; ++k) acc = fmaf(__half2float(arow[k]), (float)wrow[k], acc);
+    }
+    c[m * N + n] = __float2half_rn(acc * __half2float(scale[n]));
+}
+
+int launch_generic(const void *a, const void *wq, const void *scale, void *c, int64_t M, int64_t N, int64_t K,
+                   int64_t k_begin, int64_t k_end, int layout, cudaStream_t stream) {
+    if (M > 65535) return set_error(B200Q_UNSUPPORTED, "qlinear: M=%lld is too large for the unaligned-operand kernel", (long long)M);
+    dim3 grid((unsigned)ceil_div(N, kGenericThreads), (unsigned)M, 1);
+    qlinear_generic_kernel<<<grid, kGenericThreads, 0, stream>>>(static_cast<const __half *>(a), static_cast<const int8_t *>(wq),
+                                                                 static_cast<const __half *>(scale), static_cast<__half *>(c), M, N,
+                                                                 K, k_begin, k_end, layout);
+    B200Q_CHECK_LAUNCH("qlinear_generic_kernel");
+    return B200Q_OK;
+}
+
+int check_qlinear_args(const char *op, const void *a, const void *wq, const void *scale, const void *c, int64_t M, int64_t N,
+                       int64_t K, int layout) {
+    if (M < 0 || N < 0 || K < 0) return set_error(B200Q_INVALID_ARGUMENT, "%s: negative size M=%lld N=%lld K=%lld", op, (long long)M, (long long)N, (long long)K);
+    if (layout != B200Q_LAYOUT_KN && layout != B200Q_LAYOUT_NK) return set_error(B200Q_INVALID_ARGUMENT, "%s: unknown weight layout %d", op, layout);
+    if (M > 0 && N > 0 && (c == nullptr || scale == nullptr)) return set_error(B200Q_INVALID_ARGUMENT, "%s: null output or scale pointer", op);
+    if (M > 0 && N > 0 && K > 0 && (a == nullptr || wq == nullptr)) return set_error(B200Q_INVALID_ARGUMENT, "%s: null input pointer", op);
+    if (M > 2147483647LL || N > 2147483647LL || K > 2147483647LL) return set_error(B200Q_UNSUPPORTED, "%s: sizes beyond 2^31-1 are not supported", op);
+    return B200Q_OK;
+}
+
+}  // namespace
+}  // namespace b200q
+
+extern "C" {
+
+B200Q_API size_t b200q_qlinear_workspace_bytes(int64_t M, int64_t N, int64_t K, int w_layout) {
+    using namespace b200q;
+    (void)w_layout;
+    if (M <= 0 || N <= 0 || K <= 0) return 0;
+    const DecodePlan pl = plan_decode(M, N, K);
+    return pl.counter_bytes + pl.partial_bytes;
+}
+
+B200Q_API int b200q_qlinear_f16_i8(const void *a, const void *wq, const void *scale, void *c, int64_t M, int64_t N,
+                                   int64_t K, int w_layout, void *workspace, size_t workspace_bytes, void *stream) {
+    using namespace b200q;
+    int rc = check_qlinear_args("qlinear_f16_i8", a, wq, scale, c, M, N, K, w_layout);
+    if (rc != B200Q_OK) return rc;
+    if (M == 0 || N == 0) return B200Q_OK;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    if (K == 0) {  // an empty sum
+        B200Q_CUDA_TRY(cudaMemsetAsync(c, 0, (size_t)M * N * sizeof(__half), s));
+        return B200Q_OK;
+    }
+    if (w_layout == B200Q_LAYOUT_KN && decode_kn_supported(a, wq, N, K)) {
+        return launch_decode_kn(a, wq, scale, c, M, N, K, 0, K, true, workspace, workspace_bytes, s);
+    }
+    return launch_generic(a, wq, scale, c, M, N, K, 0, K, w_layout, s);
+}
+
+B200Q_API int b200q_qlinear_f16_i8_parts(const void *a, const void *wq, const void *scale, void *c, int64_t M,
+                                         int64_t N, int64_t K, int k_parts, void *stream) {
+    using namespace b200q;
+    int rc = check_qlinear_args("qlinear_f16_i8_parts", a, wq, scale, c, M, N, K, B200Q_LAYOUT_KN);
+    if (rc != B200Q_OK) return rc;
+    if (k_parts < 1) return set_error(B200Q_INVALID_ARGUMENT, "qlinear_f16_i8_parts: k_parts must be >= 1, got %d", k_parts);
+    if (M == 0 || N == 0) return B200Q_OK;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    // Part extent of the reference's schedule: ceil(ceil(K / parts) / 8) * 8
+    // (python/hidet/graph/ops/quant/matmul_f16_i8.py:165).
+    const int64_t extent = round_up(ceil_div(K, k_parts), 8);
+    const bool fast = decode_kn_supported(a, wq, N, K);
+    for (int part = 0; part < k_parts; ++part) {
+        __half *cp = static_cast<__half *>(c) + (size_t)part * M * N;
+        const int64_t k_begin = (int64_t)part * extent;
+        int64_t k_end = k_begin + extent;
+        if (k_end > K) k_end = K;
+        if (k_begin >= K) {
+            B200Q_CUDA_TRY(cudaMemsetAsync(cp, 0, (size_t)M * N * sizeof(__half), s));
+            continue;
+        }
+        rc = fast ? launch_decode_kn(a, wq, scale, cp, M, N, K, k_begin, k_end, false, nullptr, 0, s)
+                  : launch_generic(a, wq, scale, cp, M, N, K, k_begin, k_end, B200Q_LAYOUT_KN, s);
+        if (rc != B200Q_OK) return rc;
+    }
+    return B200Q_OK;
+}
+
+}  // extern "C"

@@ -1,0 +1,458 @@
+// Symmetric quantize / dequantize kernels.
+//
+// The arithmetic repeats, operation for operation, what the reference's generated kernels do for
+// SymmetricQuantizationTask / SymmetricDeQuantizationTask (python/hidet/graph/ops/quant/symmetric.py:23-61):
+//
+//     x     = (0 <= w) ? w : -w
+//     amax  = max over the reduced dimension of x, starting from the lowest finite value
+//     scale = amax / (T)qmax
+//     wq    = (Q) round(w / scale)          round = hrint for f16 / bf16, roundf for f32
+//     w'    = (T) wq * scale
+//
+// in w's own type T, with CUDA's own operators for __half / __nv_bfloat16 (their division is an
+// approximate reciprocal times the dividend, rounded once; that is part of the result).  This file
+// is compiled with -ftz=true -prec-div=false, the flags the reference compiles its kernels with
+// (python/hidet/backend/build.py:142-177), because they decide the f32 division.
+//
+// What differs from the reference is the schedule: the reference reads the weight twice from HBM
+// with one thread per column walking K serially; here a thread-block cluster owns a panel of
+// columns, each CTA keeps its slice of the panel in shared memory, partial maxima are exchanged
+// through distributed shared memory, and the slice is quantized from shared memory, so the weight
+// crosses HBM once.  max is exact and order-independent, so the result does not depend on the
+// schedule.
+#include <cooperative_groups.h>
+#include <cfloat>
+
+#include "common.cuh"
+
+namespace cg = cooperative_groups;
+
+namespace b200q {
+namespace {
+
+// ---------------------------------------------------------------------------------------------
+// per-type arithmetic, spelled the way the reference's generated code spells it
+// ---------------------------------------------------------------------------------------------
+template <typename T>
+struct Arith;
+
+template <>
+struct Arith<__half> {
+    static __device__ __forceinline__ __half lowest() { return (__half)-65504.0f; }
+    static __device__ __forceinline__ __half abs_(__half w) { return ((__half)0.0f <= w) ? w : (-w); }
+    static __device__ __forceinline__ __half max_(__half a, __half b) { return __hmax(a, b); }
+    static __device__ __forceinline__ __half div_(__half a, __half b) { return a / b; }
+    static __device__ __forceinline__ __half qmax(int q) { return (__half)(float)q; }
+    template <typename Q>
+    static __device__ __forceinline__ Q quant(__half w, __half scale) {
+        return (Q)(short)(hrint(w / scale));
+    }
+    template <typename Q>
+    static __device__ __forceinline__ __half dequant(Q q, __half scale) {
+        return __short2half_rn((short)q) * scale;
+    }
+};
+
+template <>
+struct Arith<__nv_bfloat16> {
+    static __device__ __forceinline__ __nv_bfloat16 lowest() { return (__nv_bfloat16)-3.4e+38f; }
+    static __device__ __forceinline__ __nv_bfloat16 abs_(__nv_bfloat16 w) { return ((__nv_bfloat16)0.0f <= w) ? w : (-w); }
+    static __device__ __forceinline__ __nv_bfloat16 max_(__nv_bfloat16 a, __nv_bfloat16 b) { return __hmax(a, b); }
+    static __device__ __forceinline__ __nv_bfloat16 div_(__nv_bfloat16 a, __nv_bfloat16 b) { return a / b; }
+    static __device__ __forceinline__ __nv_bfloat16 qmax(int q) { return (__nv_bfloat16)(float)q; }
+    template <typename Q>
+    static __device__ __forceinline__ Q quant(__nv_bfloat16 w, __nv_bfloat16 scale) {
+        return (Q)(hrint(w / scale));
+    }
+    template <typename Q>
+    static __device__ __forceinline__ __nv_bfloat16 dequant(Q q, __nv_bfloat16 scale) {
+        return __short2bfloat16_rn((short)q) * scale;
+    }
+};
+
+template <>
+struct Arith<float> {
+    static __device__ __forceinline__ float lowest() { return -3.4028234663852886e+38f; }
+    static __device__ __forceinline__ float abs_(float w) { return (0.0f <= w) ? w : (-w); }
+    static __device__ __forceinline__ float max_(float a, float b) { return fmaxf(a, b); }
+    static __device__ __forceinline__ float div_(float a, float b) { return a / b; }
+    static __device__ __forceinline__ float qmax(int q) { return (float)q; }
+    template <typename Q>
+    static __device__ __forceinline__ Q quant(float w, float scale) {
+        return (Q)(roundf(w / scale));
+    }
+    template <typename Q>
+    static __device__ __forceinline__ float dequant(Q q, float scale) {
+        return ((float)q) * scale;
+    }
+};
+
+template <typename Q>
+struct QMax;
+template <>
+struct QMax<int8_t> {
+    static constexpr int value = 127;
+};
+template <>
+struct QMax<int16_t> {
+    static constexpr int value = 32767;
+};
+
+// N elements of T moved as one naturally aligned vector.
+template <typename T, int N>
+struct alignas(sizeof(T) * N) Vec {
+    T v[N];
+};
+
+template <typename T, int N>
+__device__ __forceinline__ Vec<T, N> load_vec(const T *p) {
+    return *reinterpret_cast<const Vec<T, N> *>(p);
+}
+template <typename T, int N>
+__device__ __forceinline__ void store_vec(T *p, const Vec<T, N> &x) {
+    *reinterpret_cast<Vec<T, N> *>(p) = x;
+}
+
+constexpr int kThreads = 256;
+
+// ---------------------------------------------------------------------------------------------
+// reduce over rows (Hidet dims=0): scale[cols]
+// ---------------------------------------------------------------------------------------------
+// grid = (cluster_size, panels); the CTAs of one cluster share blockIdx.y (a panel of TX*VEC
+// columns) and split the rows.  cache != 0: the CTA's rows of the panel are kept in dynamic shared
+// memory between the two phases; cache == 0: phase 2 reads them again from global memory.
+template <typename T, typename Q, int VEC>
+__global__ void __launch_bounds__(kThreads) quantize_cols_kernel(const T *__restrict__ w, Q *__restrict__ wq,
+                                                                 T *__restrict__ scale, int64_t rows, int64_t cols,
+                                                                 int64_t rows_per_cta, int cache) {
+    constexpr int TX = (VEC == 1) ? 32 : 8;    // threads across a panel row
+    constexpr int TY = kThreads / TX;          // rows per sweep
+    constexpr int PW = TX * VEC;               // panel width in elements
+    using A = Arith<T>;
+
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    __shared__ T red[TY][PW];
+    __shared__ T part[PW];
+    __shared__ T amax_s[PW];
+
+    T *tile = reinterpret_cast<T *>(smem_raw);
+
+    cg::cluster_group cluster = cg::this_cluster();
+    const int tx = threadIdx.x % TX;
+    const int ty = threadIdx.x / TX;
+    const int64_t col = (int64_t)blockIdx.y * PW + (int64_t)tx * VEC;
+    const bool col_ok = col < cols;            // cols % VEC == 0 whenever VEC > 1
+    const int64_t row0 = (int64_t)blockIdx.x * rows_per_cta;
+    int64_t nrows = rows - row0;
+    if (nrows > rows_per_cta) nrows = rows_per_cta;
+    if (nrows < 0) nrows = 0;
+
+    // ---- phase 1: partial absmax of this CTA's rows ----
+    T m[VEC];
+#pragma unroll
+    for (int i = 0; i < VEC; ++i) m[i] = A::lowest();
+    if (col_ok) {
+        const T *src = w + row0 * cols + col;
+#pragma unroll 4
+        for (int64_t r = ty; r < nrows; r += TY) {
+            Vec<T, VEC> x = load_vec<T, VEC>(src + r * cols);
+            if (cache) store_vec<T, VEC>(tile + r * PW + tx * VEC, x);
+#pragma unroll
+            for (int i = 0; i < VEC; ++i) m[i] = A::max_(m[i], A::abs_(x.v[i]));
+        }
+    }
+#pragma unroll
+    for (int i = 0; i < VEC; ++i) red[ty][tx * VEC + i] = m[i];
+    __syncthreads();
+    if (threadIdx.x < PW) {
+        T a = A::lowest();
+#pragma unroll
+        for (int j = 0; j < TY; ++j) a = A::max_(a, red[j][threadIdx.x]);
+        part[threadIdx.x] = a;
+    }
+    // ---- exchange partial maxima inside the cluster ----
+    cluster.sync();
+    if (threadIdx.x < PW) {
+        T a = A::lowest();
+        const unsigned int n = cluster.num_blocks();
+        for (unsigned int r = 0; r < n; ++r) {
+            const T *remote = cluster.map_shared_rank(part, r);
+            a = A::max_(a, remote[threadIdx.x]);
+        }
+        amax_s[threadIdx.x] = a;
+    }
+    cluster.sync();  // nobody leaves (or overwrites part) while a peer may still read it
+
+    // ---- phase 2: scale and quantize ----
+    const T qm = A::qmax(QMax<Q>::value);
+    if (blockIdx.x == 0 && threadIdx.x < PW) {
+        const int64_t c = (int64_t)blockIdx.y * PW + threadIdx.x;
+        if (c < cols) scale[c] = A::div_(amax_s[threadIdx.x], qm);
+    }
+    if (col_ok) {
+        T s[VEC];
+#pragma unroll
+        for (int i = 0; i < VEC; ++i) s[i] = A::div_(amax_s[tx * VEC + i], qm);
+        const T *src = w + row0 * cols + col;
+        Q *dst = wq + row0 * cols + col;
+#pragma unroll 4
+        for (int64_t r = ty; r < nrows; r += TY) {
+            Vec<T, VEC> x = cache ? load_vec<T, VEC>(tile + r * PW + tx * VEC) : load_vec<T, VEC>(src + r * cols);
+            Vec<Q, VEC> q;
+#pragma unroll
+            for (int i = 0; i < VEC; ++i) q.v[i] = A::template quant<Q>(x.v[i], s[i]);
+            store_vec<Q, VEC>(dst + r * cols, q);
+        }
+    }
+}
+
+// ---------------------------------------------------------------------------------------------
+// reduce over columns (Hidet dims=-1): scale[rows]; one CTA per row, warp-shuffle reduction
+// ---------------------------------------------------------------------------------------------
+template <typename T>
+__device__ __forceinline__ T warp_max(T a) {
+    using A = Arith<T>;
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) a = A::max_(a, __shfl_xor_sync(0xffffffffu, a, off));
+    return a;
+}
+
+// REG_CHUNKS: vectors of the row each thread keeps in registers between the two phases; rows longer
+// than blockDim * VEC * REG_CHUNKS read the remainder again (it is in L1/L2 by then).
+template <typename T, typename Q, int VEC, int REG_CHUNKS>
+__global__ void __launch_bounds__(kThreads) quantize_rows_kernel(const T *__restrict__ w, Q *__restrict__ wq,
+                                                                 T *__restrict__ scale, int64_t rows, int64_t cols) {
+    using A = Arith<T>;
+    __shared__ T warp_part[kThreads / 32];
+    __shared__ T amax_s;
+
+    const int64_t row = blockIdx.x;
+    const T *src = w + row * cols;
+    Q *dst = wq + row * cols;
+    const int64_t nvec = cols / VEC;  // cols % VEC == 0 whenever VEC > 1
+    const int64_t stride = blockDim.x;
+
+    Vec<T, VEC> keep[REG_CHUNKS];
+    T m = A::lowest();
+#pragma unroll
+    for (int j = 0; j < REG_CHUNKS; ++j) {
+        const int64_t i = threadIdx.x + j * stride;
+        if (i < nvec) {
+            keep[j] = load_vec<T, VEC>(src + i * VEC);
+#pragma unroll
+            for (int e = 0; e < VEC; ++e) m = A::max_(m, A::abs_(keep[j].v[e]));
+        }
+    }
+    for (int64_t i = threadIdx.x + REG_CHUNKS * stride; i < nvec; i += stride) {
+        Vec<T, VEC> x = load_vec<T, VEC>(src + i * VEC);
+#pragma unroll
+        for (int e = 0; e < VEC; ++e) m = A::max_(m, A::abs_(x.v[e]));
+    }
+    m = warp_max<T>(m);
+    if ((threadIdx.x & 31) == 0) warp_part[threadIdx.x >> 5] = m;
+    __syncthreads();
+    if (threadIdx.x < 32) {
+        const int nwarps = (blockDim.x + 31) >> 5;
+        T a = (threadIdx.x < nwarps) ? warp_part[threadIdx.x] : A::lowest();
+        a = warp_max<T>(a);
+        if (threadIdx.x == 0) amax_s = a;
+    }
+    __syncthreads();
+    const T s = A::div_(amax_s, A::qmax(QMax<Q>::value));
+    if (threadIdx.x == 0) scale[row] = s;
+
+#pragma unroll
+    for (int j = 0; j < REG_CHUNKS; ++j) {
+        const int64_t i = threadIdx.x + j * stride;
+        if (i < nvec) {
+            Vec<Q, VEC> q;
+#pragma unroll
+            for (int e = 0; e < VEC; ++e) q.v[e] = A::template quant<Q>(keep[j].v[e], s);
+            store_vec<Q, VEC>(dst + i * VEC, q);
+        }
+    }
+    for (int64_t i = threadIdx.x + REG_CHUNKS * stride; i < nvec; i += stride) {
+        Vec<T, VEC> x = load_vec<T, VEC>(src + i * VEC);
+        Vec<Q, VEC> q;
+#pragma unroll
+        for (int e = 0; e < VEC; ++e) q.v[e] = A::template quant<Q>(x.v[e], s);
+        store_vec<Q, VEC>(dst + i * VEC, q);
+    }
+}
+
+// ---------------------------------------------------------------------------------------------
+// dequantize: one vector of VEC quantized values per thread
+// ---------------------------------------------------------------------------------------------
+template <typename T, typename Q, int VEC>
+__global__ void __launch_bounds__(kThreads) dequantize_kernel(const Q *__restrict__ wq, const T *__restrict__ scale,
+                                                              T *__restrict__ w, int64_t rows, int64_t cols,
+                                                              int reduce_dim) {
+    using A = Arith<T>;
+    const int64_t vec_per_row = cols / VEC;
+    const int64_t total = rows * vec_per_row;
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
+        const int64_t r = i / vec_per_row;
+        const int64_t c = (i - r * vec_per_row) * VEC;
+        Vec<Q, VEC> q = load_vec<Q, VEC>(wq + r * cols + c);
+        Vec<T, VEC> out;
+        if (reduce_dim == 0) {
+            Vec<T, VEC> s = load_vec<T, VEC>(scale + c);
+#pragma unroll
+            for (int e = 0; e < VEC; ++e) out.v[e] = A::template dequant<Q>(q.v[e], s.v[e]);
+        } else {
+            const T s = scale[r];
+#pragma unroll
+            for (int e = 0; e < VEC; ++e) out.v[e] = A::template dequant<Q>(q.v[e], s);
+        }
+        store_vec<T, VEC>(w + r * cols + c, out);
+    }
+}
+
+bool aligned(const void *p, size_t a) { return (reinterpret_cast<uintptr_t>(p) % a) == 0; }
+
+// Largest dynamic shared memory a quantize_cols CTA may ask for (the static arrays need a little).
+constexpr size_t kMaxTileBytes = 200 * 1024;
+
+template <typename T, typename Q, int VEC>
+int launch_quantize_cols(const T *w, Q *wq, T *scale, int64_t rows, int64_t cols, cudaStream_t stream) {
+    constexpr int TX = (VEC == 1) ? 32 : 8;
+    constexpr int TY = kThreads / TX;
+    constexpr int PW = TX * VEC;
+    const int64_t panels = ceil_div(cols, PW);
+    if (panels > 65535) return set_error(B200Q_UNSUPPORTED, "symmetric_quantize: %lld columns exceed the grid limit", (long long)cols);
+
+    // Split the rows over the largest portable cluster that still leaves every CTA a full sweep,
+    // and keep the slice in shared memory when it fits.
+    int cluster = 8;
+    while (cluster > 1 && ceil_div(rows, cluster) < TY) cluster >>= 1;
+    const int64_t rows_per_cta = ceil_div(rows, cluster);
+    size_t tile_bytes = (size_t)rows_per_cta * PW * sizeof(T);
+    int cache = 1;
+    if (tile_bytes > kMaxTileBytes) {
+        cache = 0;
+        tile_bytes = 0;
+    }
+    auto kernel = quantize_cols_kernel<T, Q, VEC>;
+    if (tile_bytes > 48 * 1024) {
+        B200Q_CUDA_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kMaxTileBytes));
+    }
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((unsigned)cluster, (unsigned)panels, 1);
+    cfg.blockDim = dim3(kThreads, 1, 1);
+    cfg.dynamicSmemBytes = tile_bytes;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = (unsigned)cluster;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    B200Q_CUDA_TRY(cudaLaunchKernelEx(&cfg, kernel, w, wq, scale, rows, cols, rows_per_cta, cache));
+    return B200Q_OK;
+}
+
+template <typename T, typename Q, int VEC>
+int launch_quantize_rows(const T *w, Q *wq, T *scale, int64_t rows, int64_t cols, cudaStream_t stream) {
+    if (rows > 2147483647LL) return set_error(B200Q_UNSUPPORTED, "symmetric_quantize: %lld rows exceed the grid limit", (long long)rows);
+    const int64_t nvec = cols / VEC;
+    int threads = (int)round_up(nvec < 32 ? 32 : nvec, 32);
+    if (threads > kThreads) threads = kThreads;
+    quantize_rows_kernel<T, Q, VEC, 4><<<(unsigned)rows, threads, 0, stream>>>(w, wq, scale, rows, cols);
+    B200Q_CHECK_LAUNCH("quantize_rows_kernel");
+    return B200Q_OK;
+}
+
+template <typename T, typename Q>
+int quantize_typed(const void *w_, void *wq_, void *scale_, int64_t rows, int64_t cols, int reduce_dim, cudaStream_t stream) {
+    const T *w = static_cast<const T *>(w_);
+    Q *wq = static_cast<Q *>(wq_);
+    T *scale = static_cast<T *>(scale_);
+    constexpr int VEC = 16 / sizeof(T);
+    const bool vec_ok = (cols % VEC == 0) && aligned(w, 16) && aligned(wq, VEC * sizeof(Q));
+    if (reduce_dim == 0) {
+        return vec_ok ? launch_quantize_cols<T, Q, VEC>(w, wq, scale, rows, cols, stream)
+                      : launch_quantize_cols<T, Q, 1>(w, wq, scale, rows, cols, stream);
+    }
+    return vec_ok ? launch_quantize_rows<T, Q, VEC>(w, wq, scale, rows, cols, stream)
+                  : launch_quantize_rows<T, Q, 1>(w, wq, scale, rows, cols, stream);
+}
+
+template <typename T, typename Q>
+int dequantize_typed(const void *wq_, const void *scale_, void *w_, int64_t rows, int64_t cols, int reduce_dim,
+                     cudaStream_t stream) {
+    const Q *wq = static_cast<const Q *>(wq_);
+    const T *scale = static_cast<const T *>(scale_);
+    T *w = static_cast<T *>(w_);
+    constexpr int VEC = 16 / sizeof(T);  // 16-byte scale / output vectors; input vector is VEC * sizeof(Q)
+    const bool vec_ok = (cols % VEC == 0) && aligned(w, 16) && aligned(wq, VEC * sizeof(Q)) && aligned(scale, 16);
+    const int64_t total = rows * (vec_ok ? cols / VEC : cols);
+    int64_t blocks = ceil_div(total, kThreads);
+    const int64_t cap = (int64_t)sm_count() * 16;
+    if (cap > 0 && blocks > cap) blocks = cap;
+    if (blocks < 1) blocks = 1;
+    if (vec_ok) {
+        dequantize_kernel<T, Q, VEC><<<(unsigned)blocks, kThreads, 0, stream>>>(wq, scale, w, rows, cols, reduce_dim);
+    } else {
+        dequantize_kernel<T, Q, 1><<<(unsigned)blocks, kThreads, 0, stream>>>(wq, scale, w, rows, cols, reduce_dim);
+    }
+    B200Q_CHECK_LAUNCH("dequantize_kernel");
+    return B200Q_OK;
+}
+
+int check_common(const char *op, const void *a, const void *b, const void *c, int64_t rows, int64_t cols, int f_type,
+                 int q_type, int reduce_dim) {
+    if (rows < 0 || cols < 0) return set_error(B200Q_INVALID_ARGUMENT, "%s: negative shape [%lld, %lld]", op, (long long)rows, (long long)cols);
+    if (f_type < B200Q_F16 || f_type > B200Q_F32) return set_error(B200Q_INVALID_ARGUMENT, "%s: unknown float type %d", op, f_type);
+    if (q_type < B200Q_I8 || q_type > B200Q_I16) return set_error(B200Q_INVALID_ARGUMENT, "%s: unknown quantized type %d", op, q_type);
+    if (reduce_dim != 0 && reduce_dim != 1) return set_error(B200Q_INVALID_ARGUMENT, "%s: reduce_dim must be 0 or 1, got %d", op, reduce_dim);
+    if (rows > 0 && cols > 0 && (a == nullptr || b == nullptr || c == nullptr)) return set_error(B200Q_INVALID_ARGUMENT, "%s: null pointer argument", op);
+    return B200Q_OK;
+}
+
+}  // namespace
+}  // namespace b200q
+
+extern "C" {
+
+B200Q_API int b200q_symmetric_quantize(const void *w, void *wq, void *scale, int64_t rows, int64_t cols, int w_type,
+                                       int q_type, int reduce_dim, void *stream) {
+    using namespace b200q;
+    int rc = check_common("symmetric_quantize", w, wq, scale, rows, cols, w_type, q_type, reduce_dim);
+    if (rc != B200Q_OK) return rc;
+    // An empty reduced dimension has no maximum; the reference cannot build that task either.
+    if (rows == 0 || cols == 0) {
+        if ((reduce_dim == 0 ? cols : rows) == 0) return B200Q_OK;  // no outputs at all
+        return set_error(B200Q_INVALID_ARGUMENT, "symmetric_quantize: empty reduction over shape [%lld, %lld]", (long long)rows, (long long)cols);
+    }
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+#define B200Q_DISPATCH_Q(T)                                                                                    \
+    (q_type == B200Q_I8 ? quantize_typed<T, int8_t>(w, wq, scale, rows, cols, reduce_dim, s)                   \
+                        : quantize_typed<T, int16_t>(w, wq, scale, rows, cols, reduce_dim, s))
+    switch (w_type) {
+        case B200Q_F16: return B200Q_DISPATCH_Q(__half);
+        case B200Q_BF16: return B200Q_DISPATCH_Q(__nv_bfloat16);
+        default: return B200Q_DISPATCH_Q(float);
+    }
+#undef B200Q_DISPATCH_Q
+}
+
+B200Q_API int b200q_symmetric_dequantize(const void *wq, const void *scale, void *w, int64_t rows, int64_t cols,
+                                         int scale_type, int q_type, int reduce_dim, void *stream) {
+    using namespace b200q;
+    int rc = check_common("symmetric_dequantize", wq, scale, w, rows, cols, scale_type, q_type, reduce_dim);
+    if (rc != B200Q_OK) return rc;
+    if (rows == 0 || cols == 0) return B200Q_OK;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+#define B200Q_DISPATCH_DQ(T)                                                                                   \
+    (q_type == B200Q_I8 ? dequantize_typed<T, int8_t>(wq, scale, w, rows, cols, reduce_dim, s)                 \
+                        : dequantize_typed<T, int16_t>(wq, scale, w, rows, cols, reduce_dim, s))
+    switch (scale_type) {
+        case B200Q_F16: return B200Q_DISPATCH_DQ(__half);
+        case B200Q_BF16: return B200Q_DISPATCH_DQ(__nv_bfloat16);
+        default: return B200Q_DISPATCH_DQ(float);
+    }
+#undef B200Q_DISPATCH_DQ
+}
+
+}  // extern "C"

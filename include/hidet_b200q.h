@@ -1,0 +1,136 @@
+/*
+ * hidet_b200q.h -- C ABI of libhidet_b200q.so
+ *
+ * Hand-written sm_100a (B200) kernels for Hidet's weight-only int8 quantized linear path:
+ * symmetric quantize / dequantize, the absmax reduction behind them, and the f16 x int8
+ * matmul that Hidet's quantization pass substitutes for fp16 matmul / linear.
+ *
+ * Conventions (they follow the reference's native runtime, src/hidet/runtime/logging.cpp:14-36
+ * and include/hidet/runtime/common.h:16-18):
+ *   - every entry point is extern "C" with default visibility, takes plain pointers and sizes,
+ *     and launches asynchronously on the CUDA stream passed as `stream` (a cudaStream_t; NULL
+ *     means the legacy default stream).  No entry point synchronises (b200q_check_status
+ *     excepted), and none allocates or frees device memory;
+ *   - the caller owns every buffer, outputs included (the reference allocates outputs before the
+ *     call too: python/hidet/runtime/compiled_task.py:146-173);
+ *   - every entry point returns a b200q_status.  On failure a thread-local message is kept and
+ *     b200q_get_last_error() returns it and clears it (read-and-clear, like
+ *     hidet_get_last_error).  Nothing aborts the process and no kernel traps.
+ *   - matrices are dense row-major.  "KN" weight layout = [K, N] with N contiguous, the layout of
+ *     the reference operator (python/hidet/graph/ops/quant/matmul.py:30-32); "NK" = [N, K] with K
+ *     contiguous, the layout torch.nn.Linear stores.
+ */
+#ifndef HIDET_B200Q_H
+#define HIDET_B200Q_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#if defined(__GNUC__)
+#define B200Q_API __attribute__((visibility("default")))
+#else
+#define B200Q_API
+#endif
+
+typedef enum b200q_status {
+    B200Q_OK = 0,
+    B200Q_INVALID_ARGUMENT = 1, /* null pointer, negative size, unknown enum value            */
+    B200Q_UNSUPPORTED = 2,      /* a legal request that this build has no kernel for          */
+    B200Q_WORKSPACE_TOO_SMALL = 3,
+    B200Q_CUDA_ERROR = 4,       /* a CUDA runtime / driver call failed; message has the text  */
+    B200Q_KERNEL_TIMEOUT = 5    /* a bounded device-side wait ran out (see b200q_check_status) */
+} b200q_status;
+
+/* element types of the floating-point side (weight before quantization, scale, dequantized weight) */
+typedef enum b200q_float_type { B200Q_F16 = 0, B200Q_BF16 = 1, B200Q_F32 = 2 } b200q_float_type;
+/* element types of the quantized side */
+typedef enum b200q_quant_type { B200Q_I8 = 0, B200Q_I16 = 1 } b200q_quant_type;
+/* memory layout of the int8 weight given to the matmul */
+typedef enum b200q_weight_layout { B200Q_LAYOUT_KN = 0, B200Q_LAYOUT_NK = 1 } b200q_weight_layout;
+
+/* Library version as major*10000 + minor*100 + patch. */
+B200Q_API int b200q_version(void);
+
+/* Message of the last failed call on this thread, or "" if none; clears it.
+ * Counterpart of hidet_get_last_error (src/hidet/runtime/logging.cpp:29-36). */
+B200Q_API const char *b200q_get_last_error(void);
+
+/*
+ * Symmetric quantization of a 2-D tensor w[rows, cols].
+ * Replaces the three generated kernels of SymmetricQuantizationTask
+ * (python/hidet/graph/ops/quant/symmetric.py:23-47): absmax reduction, scale, quantize.
+ *
+ *   reduce_dim = 0 : absmax over rows   -> scale[cols]  (Hidet dims=0, "per output channel" for a
+ *                                                         [K, N] weight; the linear rewrite uses it)
+ *   reduce_dim = 1 : absmax over cols   -> scale[rows]  (Hidet dims=-1, row-wise)
+ *
+ *   amax  = max |w|                      in w's own type
+ *   scale = amax / qmax                  qmax = 127 (int8) or 32767 (int16), in w's own type
+ *   wq    = (q_type) round(w / scale)    round = hrint (ties to even) for f16 / bf16,
+ *                                                roundf (ties away from zero) for f32
+ *
+ * The arithmetic is the reference's, operation for operation, so wq and scale are bit-identical
+ * to what the reference's kernels write.  scale has w's element type.
+ */
+B200Q_API int b200q_symmetric_quantize(const void *w, void *wq, void *scale, int64_t rows, int64_t cols,
+                                       int w_type /* b200q_float_type */, int q_type /* b200q_quant_type */,
+                                       int reduce_dim, void *stream);
+
+/*
+ * Symmetric dequantization w[r, c] = (scale_type) wq[r, c] * scale[reduce_dim == 0 ? c : r].
+ * Replaces SymmetricDeQuantizationTask (python/hidet/graph/ops/quant/symmetric.py:50-61).
+ */
+B200Q_API int b200q_symmetric_dequantize(const void *wq, const void *scale, void *w, int64_t rows, int64_t cols,
+                                         int scale_type /* b200q_float_type */, int q_type /* b200q_quant_type */,
+                                         int reduce_dim, void *stream);
+
+/*
+ * Bytes of scratch b200q_qlinear_f16_i8 needs for this problem (0 is a valid answer).
+ * The scratch must be zero-filled once before its first use; every call leaves it zero-filled in
+ * the part that has to be (its tile counters), so the same buffer can serve later calls of any
+ * shape whose requirement it covers.  Two calls that may overlap on the GPU need two buffers.
+ * Counterpart of request_cuda_workspace(nbytes, require_clean)
+ * (src/hidet/runtime/cuda/context.cpp:90-104).
+ */
+B200Q_API size_t b200q_qlinear_workspace_bytes(int64_t M, int64_t N, int64_t K, int w_layout);
+
+/*
+ * c[M, N] (f16) = a[M, K] (f16) x dequant(wq, scale), fp32 accumulation, scale applied to the fp32
+ * sum, one rounding to f16.
+ * Replaces symmetric_quant_matmul together with the resolve rule's
+ * symmetric_quant_matmul_f16_i8(...).sum(0) (python/hidet/graph/ops/quant/matmul.py:83-93,
+ * python/hidet/graph/ops/quant/resolve.py:23-100).  Leading batch dimensions of `a` are folded
+ * into M by the caller (the weight is 2-D).
+ *
+ *   wq    : int8, [K, N] if w_layout == B200Q_LAYOUT_KN, [N, K] if B200Q_LAYOUT_NK
+ *   scale : f16 [N]
+ * Picks the small-M streaming kernel or the large-M tensor-core kernel from M.
+ */
+B200Q_API int b200q_qlinear_f16_i8(const void *a, const void *wq, const void *scale, void *c, int64_t M, int64_t N,
+                                   int64_t K, int w_layout, void *workspace, size_t workspace_bytes, void *stream);
+
+/*
+ * The reference's explicit split-K form: c[p, M, N] (f16) = scale[n] * sum over the p-th K part of
+ * a[m, k] * wq[k, n], parts of ceil(K / k_parts) consecutive k (the last may be short or empty).
+ * The caller sums over p.  Replaces symmetric_quant_matmul_f16_i8
+ * (python/hidet/graph/ops/quant/matmul_f16_i8.py:28-93, 501-511).  Each part is accumulated in
+ * fp32 and rounded to f16 once.  KN layout only (the reference has no other).
+ */
+B200Q_API int b200q_qlinear_f16_i8_parts(const void *a, const void *wq, const void *scale, void *c, int64_t M,
+                                         int64_t N, int64_t K, int k_parts, void *stream);
+
+/*
+ * Device-side status word of the calling thread's current device: 0 if no bounded wait of any
+ * kernel launched so far has run out.  Synchronises the device.  A non-zero value is returned as
+ * B200Q_KERNEL_TIMEOUT with the details in the error message, and the word is cleared.
+ */
+B200Q_API int b200q_check_status(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* HIDET_B200Q_H */
