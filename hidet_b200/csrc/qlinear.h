@@ -12,6 +12,7 @@ struct DecodePlan {
     int n_tiles = 0;
     int m_tiles = 0;
     int splits = 1;            // CTAs along K per output tile
+    int cluster = 1;           // > 1: those CTAs form one thread-block cluster and need no workspace
     int iters_per_split = 0;   // 64-row k steps each of them takes
     size_t counter_bytes = 0;  // head of the workspace: one arrival counter per output tile
     size_t partial_bytes = 0;  // then [splits][M][N] fp32 partial sums (0 when splits == 1)

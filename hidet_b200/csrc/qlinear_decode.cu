@@ -12,8 +12,12 @@
 // Replaces the generated mma.sync kernel of python/hidet/graph/ops/quant/matmul_f16_i8.py:136-485
 // (f16 accumulation, 64x128 tiles, no split-K by default) for M <= 16, and serves larger M by
 // tiling M over blockIdx.z.
+#include <cooperative_groups.h>
+
 #include "common.cuh"
 #include "qlinear.h"
+
+namespace cg = cooperative_groups;
 
 namespace b200q {
 namespace decode {
@@ -32,6 +36,7 @@ constexpr int RED_BYTES = CONSUMER_WARPS * BM * RED_STRIDE * 4;
 constexpr int PIPE_BYTES = STAGES * STAGE_TX_BYTES;
 constexpr int SMEM_BYTES = (PIPE_BYTES > RED_BYTES ? PIPE_BYTES : RED_BYTES) + 1024;  // + alignment slack
 constexpr int64_t kMaxCounters = 65536;       // arrival counters at the head of the workspace
+constexpr int kMaxCluster = 8;               // largest portable cluster
 
 __device__ __forceinline__ uint32_t lds32(uint32_t addr) {
     uint32_t v;
@@ -75,7 +80,12 @@ struct Params {
     int k_begin, k_end;       // the k range this launch sums over (k_end is also the tensor maps' K extent)
     int iters_per_split;      // BK-sized k steps per split
     int splits;
+    int mode;                 // how the splits of one output tile are combined
 };
+
+constexpr int kModeDirect = 0;     // splits == 1
+constexpr int kModeCluster = 1;    // the splits of a tile form one thread-block cluster (splits <= 16)
+constexpr int kModeWorkspace = 2;  // partial tiles in the caller's workspace, last arriver sums them
 
 __global__ void __launch_bounds__(THREADS) qlinear_decode_kn_kernel(const __grid_constant__ CUtensorMap map_w,
                                                                     const __grid_constant__ CUtensorMap map_a,
@@ -207,26 +217,60 @@ __global__ void __launch_bounds__(THREADS) qlinear_decode_kn_kernel(const __grid
     int rows = p.M - m0;
     if (rows > BM) rows = BM;
     const bool active = (col < BN) && (n < p.N);
+    const int skew = col + (col >> 5);
 
-    if (p.splits == 1) {
+    if (p.mode == kModeDirect) {
         if (active) {
             const float sc = __half2float(p.scale[n]);
             for (int r = 0; r < rows; ++r) {
                 float v = 0.0f;
 #pragma unroll
-                for (int w = 0; w < CONSUMER_WARPS; ++w) v += red[(w * BM + r) * RED_STRIDE + col + (col >> 5)];
+                for (int w = 0; w < CONSUMER_WARPS; ++w) v += red[(w * BM + r) * RED_STRIDE + skew];
                 p.c[(size_t)(m0 + r) * p.N + n] = __float2half_rn(v * sc);
             }
         }
         return;
     }
 
-    // ---------------- split-K: publish the partial tile, last CTA of the tile finishes ----------------
+    if (p.mode == kModeCluster) {
+        // ---------------- split-K inside a cluster: partial tiles meet through distributed shared memory ----------------
+        // The CTAs of a cluster are the `splits` CTAs of one output tile.  Each first folds its four
+        // warp slabs into slab 0, then CTA `rank` sums columns [rank * BN / splits, ...) over all CTAs
+        // in rank order (a fixed order: the result does not depend on timing).
+        cg::cluster_group cluster = cg::this_cluster();
+        if (col < BN) {
+            for (int r = 0; r < rows; ++r) {
+                float v = 0.0f;
+#pragma unroll
+                for (int w = 0; w < CONSUMER_WARPS; ++w) v += red[(w * BM + r) * RED_STRIDE + skew];
+                red[r * RED_STRIDE + skew] = v;
+            }
+        }
+        cluster.sync();
+        const unsigned int csize = cluster.num_blocks();
+        const unsigned int rank = cluster.block_rank();
+        const int cols_per = BN / (int)csize;
+        for (int idx = threadIdx.x; idx < rows * cols_per; idx += THREADS) {
+            const int r = idx / cols_per;
+            const int cc = (int)rank * cols_per + (idx - r * cols_per);
+            const int nn = n0 + cc;
+            if (nn < p.N) {
+                const int off = r * RED_STRIDE + cc + (cc >> 5);
+                float v = 0.0f;
+                for (unsigned int j = 0; j < csize; ++j) v += cluster.map_shared_rank(red, j)[off];
+                p.c[(size_t)(m0 + r) * p.N + nn] = __float2half_rn(v * __half2float(p.scale[nn]));
+            }
+        }
+        cluster.sync();  // nobody leaves while a peer may still read its shared memory
+        return;
+    }
+
+    // ---------------- split-K through the workspace: publish the partial tile, last CTA of the tile finishes ----------------
     if (active) {
         for (int r = 0; r < rows; ++r) {
             float v = 0.0f;
 #pragma unroll
-            for (int w = 0; w < CONSUMER_WARPS; ++w) v += red[(w * BM + r) * RED_STRIDE + col + (col >> 5)];
+            for (int w = 0; w < CONSUMER_WARPS; ++w) v += red[(w * BM + r) * RED_STRIDE + skew];
             p.partial[((size_t)split * p.M + (m0 + r)) * p.N + n] = v;
         }
     }
@@ -244,6 +288,7 @@ __global__ void __launch_bounds__(THREADS) qlinear_decode_kn_kernel(const __grid
         const float sc = __half2float(p.scale[n]);
         for (int r = 0; r < rows; ++r) {
             float v = 0.0f;
+#pragma unroll 4
             for (int s = 0; s < p.splits; ++s) v += __ldcg(&p.partial[((size_t)s * p.M + (m0 + r)) * p.N + n]);
             p.c[(size_t)(m0 + r) * p.N + n] = __float2half_rn(v * sc);
         }
@@ -268,15 +313,30 @@ DecodePlan plan_decode(int64_t M, int64_t N, int64_t K) {
     const int max_splits = k_iters / 4 > 0 ? k_iters / 4 : 1;  // at least four stages of work per CTA
     if (splits > max_splits) splits = max_splits;
     if (splits > 64) splits = 64;
-    if (tiles > kMaxCounters) splits = 1;  // problems this large fill the machine without a split
     if (splits < 1) splits = 1;
+    if (splits <= 2 * kMaxCluster) {
+        // Up to a cluster's worth (and a little beyond: a full cluster beats a few more CTAs that need
+        // the workspace): the splits of a tile form a cluster and meet in distributed shared memory.
+        int c = 1;
+        while (c * 2 <= splits && c * 2 <= kMaxCluster) c *= 2;
+        splits = c;
+        pl.cluster = c;
+    } else {
+        pl.cluster = 1;
+        if (tiles > kMaxCounters) splits = 1;
+    }
     pl.iters_per_split = (int)ceil_div(k_iters, splits);
-    pl.splits = (int)ceil_div(k_iters, pl.iters_per_split);
-    if (pl.splits < 1) pl.splits = 1;
+    if (pl.cluster > 1) {
+        pl.splits = pl.cluster;  // the grid must hold whole clusters; a split may have fewer steps, or none
+    } else {
+        pl.splits = (int)ceil_div(k_iters, pl.iters_per_split);
+        if (pl.splits < 1) pl.splits = 1;
+    }
+    const bool workspace = pl.cluster == 1 && pl.splits > 1;
     // The counter region has one fixed size, so that counters never land on bytes an earlier call of
     // another shape used for partial sums: the region stays all-zero between calls.
-    pl.counter_bytes = pl.splits > 1 ? (size_t)kMaxCounters * 4 : 0;
-    pl.partial_bytes = pl.splits > 1 ? (size_t)pl.splits * M * N * 4 : 0;
+    pl.counter_bytes = workspace ? (size_t)kMaxCounters * 4 : 0;
+    pl.partial_bytes = workspace ? (size_t)pl.splits * M * N * 4 : 0;
     return pl;
 }
 
@@ -293,9 +353,11 @@ int launch_decode_kn(const void *a, const void *wq, const void *scale, void *c, 
     if (!allow_split) {
         pl.iters_per_split = (int)ceil_div(k_end - k_begin, BK);
         pl.splits = 1;
+        pl.cluster = 1;
         pl.partial_bytes = 0;
+        pl.counter_bytes = 0;
     }
-    if (pl.splits > 1 && (workspace == nullptr || workspace_bytes < pl.counter_bytes + pl.partial_bytes)) {
+    if (pl.partial_bytes > 0 && (workspace == nullptr || workspace_bytes < pl.counter_bytes + pl.partial_bytes)) {
         return set_error(B200Q_WORKSPACE_TOO_SMALL, "qlinear: workspace of %zu bytes given, %zu needed for M=%lld N=%lld K=%lld",
                          workspace_bytes, pl.counter_bytes + pl.partial_bytes, (long long)M, (long long)N, (long long)K);
     }
@@ -313,7 +375,7 @@ int launch_decode_kn(const void *a, const void *wq, const void *scale, void *c, 
     p.scale = static_cast<const __half *>(scale);
     p.c = static_cast<__half *>(c);
     p.counters = static_cast<unsigned int *>(workspace);
-    p.partial = pl.splits > 1 ? reinterpret_cast<float *>(static_cast<unsigned char *>(workspace) + pl.counter_bytes) : nullptr;
+    p.partial = pl.partial_bytes > 0 ? reinterpret_cast<float *>(static_cast<unsigned char *>(workspace) + pl.counter_bytes) : nullptr;
     p.status = device_status_word();
     p.M = (int)M;
     p.N = (int)N;
@@ -321,6 +383,7 @@ int launch_decode_kn(const void *a, const void *wq, const void *scale, void *c, 
     p.k_end = (int)k_end;
     p.iters_per_split = pl.iters_per_split;
     p.splits = pl.splits;
+    p.mode = pl.splits == 1 ? kModeDirect : (pl.cluster > 1 ? kModeCluster : kModeWorkspace);
 
     static bool attr_set[64] = {false};  // per device; a repeated set is harmless
     int dev = 0;
@@ -329,9 +392,19 @@ int launch_decode_kn(const void *a, const void *wq, const void *scale, void *c, 
         B200Q_CUDA_TRY(cudaFuncSetAttribute(qlinear_decode_kn_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
         if (dev >= 0 && dev < 64) attr_set[dev] = true;
     }
-    dim3 grid((unsigned)pl.n_tiles, (unsigned)pl.splits, (unsigned)pl.m_tiles);
-    qlinear_decode_kn_kernel<<<grid, THREADS, SMEM_BYTES, stream>>>(map_w, map_a, p);
-    B200Q_CHECK_LAUNCH("qlinear_decode_kn_kernel");
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((unsigned)pl.n_tiles, (unsigned)pl.splits, (unsigned)pl.m_tiles);
+    cfg.blockDim = dim3(THREADS, 1, 1);
+    cfg.dynamicSmemBytes = SMEM_BYTES;
+    cfg.stream = stream;
+    cudaLaunchAttribute attrs[1];
+    attrs[0].id = cudaLaunchAttributeClusterDimension;
+    attrs[0].val.clusterDim.x = 1;
+    attrs[0].val.clusterDim.y = (unsigned)pl.cluster;
+    attrs[0].val.clusterDim.z = 1;
+    cfg.attrs = attrs;
+    cfg.numAttrs = 1;
+    B200Q_CUDA_TRY(cudaLaunchKernelEx(&cfg, qlinear_decode_kn_kernel, map_w, map_a, p));
     return B200Q_OK;
 }
 

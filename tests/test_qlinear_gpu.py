@@ -135,7 +135,10 @@ def test_qlinear_power_of_two_scaling_and_column_permutation():
     a_t, wq_t, scale_t = torch.from_numpy(a).cuda(), torch.from_numpy(wq).cuda(), torch.from_numpy(scale).cuda()
     c = hidet_b200.symmetric_quant_matmul(a_t, wq_t, scale_t)
     c2 = hidet_b200.symmetric_quant_matmul(a_t * 2, wq_t, scale_t)
-    assert torch.equal(c2, c * 2)
+    # doubling is exact in every step except the last rounding of results that are subnormal in half
+    normal = c.abs() >= 2.0 ** -13
+    assert torch.equal(c2[normal], (c * 2)[normal])
+    assert ((c2.float() - 2 * c.float()).abs() <= 2.0 ** -24).all()
     perm = torch.randperm(n, generator=torch.Generator().manual_seed(1)).cuda()
     cp = hidet_b200.symmetric_quant_matmul(a_t, wq_t[:, perm].contiguous(), scale_t[perm].contiguous())
     assert torch.equal(cp, c[:, perm])
