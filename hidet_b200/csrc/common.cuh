@@ -97,16 +97,20 @@ __device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
 __device__ __forceinline__ void mbar_arrive(uint32_t bar) {
     asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
 }
+// One poll: returns true once the phase with the given parity has completed.  The thread may be
+// suspended inside the instruction for up to about `kWaitHintNs` while the phase is pending, so a
+// polling loop spends few issue slots.
+constexpr uint32_t kWaitHintNs = 2000;
 __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
     uint32_t ok;
     asm volatile(
         "{\n\t"
         ".reg .pred p;\n\t"
-        "mbarrier.try_wait.parity.shared::cta.b64 p, [%0], %1;\n\t"
-        "selp.u32 %2, 1, 0, p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t"
         "}\n"
-        : "+r"(bar), "+r"(parity), "=r"(ok)
-        :
+        : "=r"(ok)
+        : "r"(bar), "r"(parity), "r"(kWaitHintNs)
         : "memory");
     return ok != 0;
 }
@@ -114,7 +118,7 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
 // Bounded wait on an mbarrier phase.  Returns false if `limit` polls passed without the phase
 // completing; the caller then records the failure and leaves.  Each poll of try_wait already
 // blocks for a hardware-defined interval, so the limit is a time bound of the order of a second.
-constexpr uint32_t kSpinLimit = 4u << 20;
+constexpr uint32_t kSpinLimit = 1u << 20;
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, uint32_t limit = kSpinLimit) {
     for (uint32_t i = 0; i < limit; ++i) {
         if (mbar_try_wait(bar, parity)) return true;
@@ -162,6 +166,13 @@ __device__ __forceinline__ uint64_t l2_policy_evict_last() {
 __device__ __forceinline__ void fence_proxy_async_smem() {
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
 }
+
+// ---- programmatic dependent launch ----
+// launch_dependents: the next kernel in the stream may start its prologue once every CTA of this grid
+// has said so.  wait: blocks until the previous kernel in the stream has completed and its writes are
+// visible; a no-op when the kernel was not launched as a programmatic dependent.
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 
 // ---- int8 -> f16 ----
 // Four signed bytes packed in `v` -> (b0, b2) in lo and (b1, b3) in hi as exact f16 values.

@@ -12,10 +12,11 @@ struct DecodePlan {
     int n_tiles = 0;
     int m_tiles = 0;
     int splits = 1;            // CTAs along K per output tile
-    int cluster = 1;           // > 1: those CTAs form one thread-block cluster and need no workspace
+    int cluster = 1;           // of them, this many form a thread-block cluster that needs no workspace
+    int groups = 1;            // clusters per tile; > 1: the clusters meet in the workspace
     int iters_per_split = 0;   // 64-row k steps each of them takes
     size_t counter_bytes = 0;  // head of the workspace: one arrival counter per output tile
-    size_t partial_bytes = 0;  // then [splits][M][N] fp32 partial sums (0 when splits == 1)
+    size_t partial_bytes = 0;  // then [groups][M][N] fp32 partial sums (0 when groups == 1)
 };
 
 DecodePlan plan_decode(int64_t M, int64_t N, int64_t K);

@@ -1,92 +1,145 @@
 // Small-M (decode) f16 x int8 quantized linear for weights in the reference's [K, N] layout.
 //
 // The op is bound by streaming the int8 weight from HBM once, so the kernel is built around that
-// stream: a producer warp keeps a ring of TMA tile loads in flight (64 k-rows x 128 columns of
-// int8, 128B-swizzled, plus the matching 16 x 64 f16 slice of the activations), four consumer warps
-// take 16 k-rows each, turn int8 pairs into exact f16 pairs in registers and feed warp-level
-// m16n8k16 tensor-core MMAs with fp32 accumulators (M <= 16 fills one MMA row block; rows beyond M
-// are zero-filled by TMA).  K is split across CTAs to fill the machine; partial sums meet in a
-// caller-provided fp32 workspace and the last CTA of a column tile adds them in a fixed order,
-// applies the per-column scale and rounds to f16 once.  The result is deterministic.
+// stream.  A producer warp keeps a ring of TMA tile loads in flight: 64 k-rows x 128 columns of int8,
+// 128B-swizzled, plus the matching 16 x 64 f16 slice of the activations.  Four consumer warps own 32
+// columns each, so no sum ever crosses a warp.  A consumer fetches its slice with transposing matrix
+// loads (four consecutive k of one column per register), turns the bytes into exact f16 pairs in
+// registers and feeds warp-level m16n8k16 tensor-core MMAs with fp32 accumulators; the weight
+// is the MMA's 16-row operand and the activations its 8-column operand, so up to 8 activation rows
+// cost one MMA per 16 x 16 weight block and up to 16 rows two (rows beyond M are zero-filled by TMA).
+//
+// K is split across CTAs to fill the machine.  Up to 16 splits of one output tile form a thread-block
+// cluster: every CTA stores its partial tile into the shared memory of the CTA that owns those
+// columns, one cluster barrier later the owner adds the partials in rank order, applies the per-column
+// scale and rounds to f16 once.  More splits than a cluster holds go through a caller-provided fp32
+// workspace, where the last CTA of a tile to arrive does the same.  Either way the order of every sum
+// is fixed, so results are the same on every run.
+//
+// The kernel is launched as a programmatic dependent of the kernel before it in the stream: weight
+// tiles do not depend on that kernel, so they are requested before waiting for it, and the kernel after
+// this one is allowed to start once the main loop is over.
 //
 // Replaces the generated mma.sync kernel of python/hidet/graph/ops/quant/matmul_f16_i8.py:136-485
 // (f16 accumulation, 64x128 tiles, no split-K by default) for M <= 16, and serves larger M by
 // tiling M over blockIdx.z.
-#include <cooperative_groups.h>
+#include <cstdlib>
 
 #include "common.cuh"
 #include "qlinear.h"
 
-namespace cg = cooperative_groups;
-
 namespace b200q {
+#ifdef B200Q_TRACE
+unsigned long long *g_trace = nullptr;
+__device__ __forceinline__ unsigned long long gtime() { unsigned long long t; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t)); return t; }
+#define TRACE(slot) do { if (p.trace && threadIdx.x == 0) p.trace[((blockIdx.z * gridDim.y + blockIdx.y) * gridDim.x + blockIdx.x) % 8192 * 8 + (slot)] = gtime(); } while (0)
+#else
+#define TRACE(slot) do {} while (0)
+#endif
 namespace decode {
 
 constexpr int BN = 128;                      // columns per CTA
 constexpr int BK = 64;                       // k rows per pipeline stage
-constexpr int BM = 16;                       // activation rows per CTA (one MMA row block)
-constexpr int STAGES = 4;
-constexpr int CONSUMER_WARPS = 4;            // each takes BK / 4 = 16 k-rows of a stage
+constexpr int BM = 16;                       // activation rows per CTA
+#ifndef B200Q_DECODE_STAGES
+#define B200Q_DECODE_STAGES 4
+#endif
+constexpr int STAGES = B200Q_DECODE_STAGES;
+constexpr int CONSUMER_WARPS = 4;            // each owns BN / 4 = 32 columns
 constexpr int THREADS = 32 * (CONSUMER_WARPS + 1);
 constexpr int W_STAGE_BYTES = BK * BN;       // 8192
 constexpr int A_STAGE_BYTES = BM * BK * 2;   // 2048
-constexpr int STAGE_TX_BYTES = W_STAGE_BYTES + A_STAGE_BYTES;
-constexpr int RED_STRIDE = BN + 4;           // fp32 words per row of the cross-warp reduction buffer
-constexpr int RED_BYTES = CONSUMER_WARPS * BM * RED_STRIDE * 4;
-constexpr int PIPE_BYTES = STAGES * STAGE_TX_BYTES;
-constexpr int SMEM_BYTES = (PIPE_BYTES > RED_BYTES ? PIPE_BYTES : RED_BYTES) + 1024;  // + alignment slack
-constexpr int64_t kMaxCounters = 65536;       // arrival counters at the head of the workspace
-constexpr int kMaxCluster = 8;               // largest portable cluster
+constexpr int PIPE_BYTES = STAGES * (W_STAGE_BYTES + A_STAGE_BYTES);
+constexpr int RECV_BYTES = BM * BN * 4;      // partial tiles pushed by the CTAs of the cluster: [rank][row][BN / ranks] fp32
+constexpr int SMEM_BYTES = PIPE_BYTES + RECV_BYTES + 1024;  // + alignment slack
+constexpr int kCtasPerSm = 4;                // resident CTAs per SM the plan aims at
+constexpr int64_t kMaxCounters = 65536;      // arrival counters at the head of the workspace
+constexpr int kMaxCluster = 8;               // largest cluster a B200 schedules (8 is the portable limit)
 
-__device__ __forceinline__ uint32_t lds32(uint32_t addr) {
-    uint32_t v;
-    asm volatile("ld.shared.b32 %0, [%1];" : "=r"(v) : "r"(addr));
-    return v;
-}
-__device__ __forceinline__ uint4 lds128(uint32_t addr) {
-    uint4 v;
-    asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr));
+__device__ __forceinline__ uint2 lds64(uint32_t addr) {
+    uint2 v;
+    asm volatile("ld.shared.v2.b32 {%0, %1}, [%2];" : "=r"(v.x), "=r"(v.y) : "r"(addr));
     return v;
 }
 
-__device__ __forceinline__ void mma_m16n8k16(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+// Two 16 x 16 byte tiles, transposed on the way to registers.  Lanes 0-15 give the addresses of the 16
+// rows (16 bytes each) of the first tile, lanes 16-31 those of the second.  With a tile stored as
+// [k][column], lane (g = lane / 4, t = lane % 4) receives, for tile i, in r[2i] the bytes
+// (k = 4t .. 4t+3, column g) and in r[2i+1] the bytes (k = 4t .. 4t+3, column g + 8): four consecutive
+// k of one column per register, the packing an MMA operand wants.
+__device__ __forceinline__ void ldmatrix_x2_trans_b8(uint32_t (&r)[4], uint32_t addr) {
+    asm volatile("ldmatrix.sync.aligned.m16n16.x2.trans.shared.b8 {%0, %1, %2, %3}, [%4];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
+                 : "r"(addr));
+}
+
+// Four signed bytes (b0 .. b3) -> f16 pairs (b0, b1) and (b2, b3), exactly.  b ^ 0x80 = b + 128 as an
+// unsigned byte u; the half with bits 0x6400 | u is 1024 + u; subtracting 1152 leaves b.
+__device__ __forceinline__ void cvt_s8x4_to_f16_pairs(uint32_t v, uint32_t &p01, uint32_t &p23) {
+    const uint32_t u = v ^ 0x80808080u;
+    const uint32_t e01 = __byte_perm(u, 0x64646464u, 0x4140);  // u0 0x64 u1 0x64
+    const uint32_t e23 = __byte_perm(u, 0x64646464u, 0x4342);  // u2 0x64 u3 0x64
+    const uint32_t bias = 0x64806480u;                          // f16x2 (1152, 1152)
+    asm("sub.f16x2 %0, %1, %2;" : "=r"(p01) : "r"(e01), "r"(bias));
+    asm("sub.f16x2 %0, %1, %2;" : "=r"(p23) : "r"(e23), "r"(bias));
+}
+
+// D[16 x 8] += A[16 x 16] * B[16 x 8]: A row-major (here: 16 weight columns x 16 k), B column-major
+// (here: 16 k x 8 activation rows).
+__device__ __forceinline__ void mma_m16n8k16(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0,
+                                             uint32_t b1) {
     asm volatile(
         "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, {%0, %1, %2, %3};"
         : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
-        : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
 
-// Two k-rows of 16 int8 columns each (x: row k, y: row k+1) -> for every column i of the 16 the f16
-// pair (w[k][i], w[k+1][i]), which is one B-fragment register of an m16n8k16 MMA.
-__device__ __forceinline__ void rows_to_pairs(const uint4 &x, const uint4 &y, uint32_t (&out)[16]) {
-    const uint32_t xs[4] = {x.x, x.y, x.z, x.w};
-    const uint32_t ys[4] = {y.x, y.y, y.z, y.w};
-#pragma unroll
-    for (int j = 0; j < 4; ++j) {
-        const uint32_t p = __byte_perm(xs[j], ys[j], 0x5410);  // x.b0 x.b1 y.b0 y.b1
-        const uint32_t q = __byte_perm(xs[j], ys[j], 0x7632);  // x.b2 x.b3 y.b2 y.b3
-        cvt_s8x4_to_f16x4(p, out[4 * j + 0], out[4 * j + 1]);
-        cvt_s8x4_to_f16x4(q, out[4 * j + 2], out[4 * j + 3]);
-    }
+// ---- cluster primitives (a kernel launched without a cluster is a cluster of one) ----
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+    uint32_t r;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+    return r;
 }
+__device__ __forceinline__ uint32_t cluster_nctarank() {
+    uint32_t r;
+    asm volatile("mov.u32 %0, %%cluster_nctarank;" : "=r"(r));
+    return r;
+}
+__device__ __forceinline__ void cluster_arrive_relaxed() { asm volatile("barrier.cluster.arrive.relaxed.aligned;" ::: "memory"); }
+__device__ __forceinline__ void cluster_arrive_release() { asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory"); }
+__device__ __forceinline__ void cluster_wait_acquire() { asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory"); }
+// Address of the same shared-memory location in CTA `rank` of the cluster.
+__device__ __forceinline__ uint32_t map_to_rank(uint32_t local_addr, uint32_t rank) {
+    uint32_t r;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(local_addr), "r"(rank));
+    return r;
+}
+__device__ __forceinline__ void st_cluster_f32(uint32_t addr, float v) {
+    asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(addr), "f"(v) : "memory");
+}
+
+constexpr int kModeDirect = 0;  // one CTA per output tile
+constexpr int kModeSplit = 1;   // `splits` CTAs per tile: clusters of `cluster` CTAs, `groups` clusters per tile
 
 struct Params {
     const __half *scale;
     __half *c;
-    float *partial;           // [splits][M][N] fp32, used when splits > 1
-    unsigned int *counters;   // [m_tiles * n_tiles], zero on entry, zero on exit
+    float *partial;           // [groups][M][N] fp32 in the workspace, used when groups > 1
+    unsigned int *counters;   // [m_tiles * n_tiles * cluster] in the workspace, zero on entry, zero on exit
     unsigned int *status;
     int M, N;
     int k_begin, k_end;       // the k range this launch sums over (k_end is also the tensor maps' K extent)
     int iters_per_split;      // BK-sized k steps per split
-    int splits;
-    int mode;                 // how the splits of one output tile are combined
+    int groups;               // clusters per output tile (splits = groups * cluster size)
+    int mode;                 // kModeDirect or kModeSplit
+#ifdef B200Q_TRACE
+    unsigned long long *trace;
+    int skip_compute;
+#endif
 };
 
-constexpr int kModeDirect = 0;     // splits == 1
-constexpr int kModeCluster = 1;    // the splits of a tile form one thread-block cluster (splits <= 16)
-constexpr int kModeWorkspace = 2;  // partial tiles in the caller's workspace, last arriver sums them
-
+// MT: 8-row blocks of activations per CTA (1: up to 8 rows, 2: up to 16).
+template <int MT>
 __global__ void __launch_bounds__(THREADS) qlinear_decode_kn_kernel(const __grid_constant__ CUtensorMap map_w,
                                                                     const __grid_constant__ CUtensorMap map_a,
                                                                     const Params p) {
@@ -100,9 +153,13 @@ __global__ void __launch_bounds__(THREADS) qlinear_decode_kn_kernel(const __grid
     unsigned char *smem_gen = smem_dyn + (smem_base - smem_u32(smem_dyn));
     const uint32_t w_base = smem_base;
     const uint32_t a_base = smem_base + STAGES * W_STAGE_BYTES;
+    const uint32_t recv_base = smem_base + PIPE_BYTES;
+    float *recv = reinterpret_cast<float *>(smem_gen + PIPE_BYTES);
 
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
+    const int g = lane >> 2;  // MMA group id
+    const int t = lane & 3;   // thread in group
     const int n0 = blockIdx.x * BN;
     const int split = blockIdx.y;
     const int m0 = blockIdx.z * BM;
@@ -112,21 +169,27 @@ __global__ void __launch_bounds__(THREADS) qlinear_decode_kn_kernel(const __grid
     if (n_iters > p.iters_per_split) n_iters = p.iters_per_split;
     if (n_iters < 0) n_iters = 0;
 
+    TRACE(0);
     if (threadIdx.x == 0) {
 #pragma unroll
         for (int s = 0; s < STAGES; ++s) {
-            mbar_init(smem_u32(&full_bar[s]), 1);
+            mbar_init(smem_u32(&full_bar[s]), 2);  // one arrival for the weight tile, one for the activation tile
             mbar_init(smem_u32(&empty_bar[s]), CONSUMER_WARPS);
         }
         mbar_fence_init();
     }
     __syncthreads();
+    // First half of a cluster barrier whose second half sits in front of the first remote store: by
+    // then every CTA of the cluster has started, which remote shared-memory access requires.
+    cluster_arrive_relaxed();
 
-    float acc[16][4];
+    // acc[j][mt][.]: 16 x 8 tile j of this warp's 32 columns, activation rows 8 * mt ... 8 * mt + 7.
+    // Element (column 16 j + 8 h + g, row 8 mt + 2t + e) is acc[j][mt][2h + e].
+    float acc[2][MT][4];
 #pragma unroll
-    for (int i = 0; i < 16; ++i) {
-        acc[i][0] = acc[i][1] = acc[i][2] = acc[i][3] = 0.0f;
-    }
+    for (int j = 0; j < 2; ++j)
+#pragma unroll
+        for (int mt = 0; mt < MT; ++mt) acc[j][mt][0] = acc[j][mt][1] = acc[j][mt][2] = acc[j][mt][3] = 0.0f;
 
     if (warp == CONSUMER_WARPS) {
         // ---------------- producer: one lane drives TMA ----------------
@@ -134,166 +197,197 @@ __global__ void __launch_bounds__(THREADS) qlinear_decode_kn_kernel(const __grid
             tma_prefetch_desc(&map_w);
             tma_prefetch_desc(&map_a);
             const uint64_t stream_policy = l2_policy_evict_first();  // the weight is read once
-            for (int it = 0; it < n_iters; ++it) {
+            const int prologue = n_iters < STAGES ? n_iters : STAGES;
+            // The weight does not depend on the kernel before this one in the stream; the activations
+            // may.  Ask for the first weight tiles, then wait for that kernel, then ask for activations.
+            for (int it = 0; it < prologue; ++it) {
+                const uint32_t bar = smem_u32(&full_bar[it]);
+                mbar_expect_tx(bar, W_STAGE_BYTES);
+                tma_load_2d_hint(w_base + it * W_STAGE_BYTES, &map_w, n0, p.k_begin + (it_begin + it) * BK, bar, stream_policy);
+            }
+            pdl_wait();
+            for (int it = 0; it < prologue; ++it) {
+                const uint32_t bar = smem_u32(&full_bar[it]);
+                mbar_expect_tx(bar, A_STAGE_BYTES);
+                tma_load_2d(a_base + it * A_STAGE_BYTES, &map_a, p.k_begin + (it_begin + it) * BK, m0, bar);
+            }
+            for (int it = STAGES; it < n_iters; ++it) {
                 const int s = it % STAGES;
-                if (it >= STAGES) {
-                    if (!mbar_wait(smem_u32(&empty_bar[s]), ((it / STAGES) - 1) & 1)) {
-                        report_timeout(p.status, kKernelDecode, 1);
-                        break;
-                    }
+                if (!mbar_wait(smem_u32(&empty_bar[s]), ((it / STAGES) - 1) & 1)) {
+                    report_timeout(p.status, kKernelDecode, 1);
+                    break;
                 }
                 const uint32_t bar = smem_u32(&full_bar[s]);
                 const int k0 = p.k_begin + (it_begin + it) * BK;
-                mbar_expect_tx(bar, STAGE_TX_BYTES);
+                mbar_expect_tx(bar, W_STAGE_BYTES);
                 tma_load_2d_hint(w_base + s * W_STAGE_BYTES, &map_w, n0, k0, bar, stream_policy);
+                mbar_expect_tx(bar, A_STAGE_BYTES);
                 tma_load_2d(a_base + s * A_STAGE_BYTES, &map_a, k0, m0, bar);
             }
+        } else {
+            pdl_wait();
         }
     } else {
         // ---------------- consumers ----------------
-        const int g = lane >> 2;  // MMA group id: activation row / B column
-        const int t = lane & 3;   // thread in group: k pair
-        const int r_lo = warp * 16 + 2 * t;  // this thread's k-rows inside a stage: r_lo, +1, +8, +9
-        // 16-byte chunk g of row r sits at chunk (g ^ (r & 7)) under the 128B swizzle.
-        const uint32_t off_x0 = (r_lo + 0) * 128 + ((g ^ ((r_lo + 0) & 7)) << 4);
-        const uint32_t off_y0 = (r_lo + 1) * 128 + ((g ^ ((r_lo + 1) & 7)) << 4);
-        const uint32_t off_x1 = (r_lo + 8) * 128 + ((g ^ ((r_lo + 8) & 7)) << 4);
-        const uint32_t off_y1 = (r_lo + 9) * 128 + ((g ^ ((r_lo + 9) & 7)) << 4);
-        // activations: rows g and g+8 (both have row & 7 == g), k = 16*warp + 2t (+8): chunks 2*warp, 2*warp+1
-        const uint32_t off_a0 = g * 128 + (((2 * warp + 0) ^ g) << 4) + 4 * t;
-        const uint32_t off_a2 = g * 128 + (((2 * warp + 1) ^ g) << 4) + 4 * t;
-        bool ok = true;
+        pdl_wait();
+        // Weights: one transposing matrix load per 16 k-rows brings this warp's 32 columns (16-byte
+        // chunks 2 warp and 2 warp + 1 of each row).  Lane l addresses row (l & 15) of chunk
+        // 2 warp + (l >> 4); under the 128B swizzle chunk c of row r sits at chunk c ^ (r & 7).
+        const uint32_t off_w = (lane & 15) * 128 + (((2 * warp + (lane >> 4)) ^ (lane & 7)) << 4);
+        // Activations: row g (and g + 8, same swizzle phase), k = 16 ks + 4t .. 4t+3: bytes 8 (t & 1) of
+        // chunk 2 ks + (t >> 1).
+        const uint32_t off_a = g * 128 + 8 * (t & 1);
+        const uint32_t a_chunk = (uint32_t)(t >> 1) ^ (uint32_t)g;  // chunk index is (2 ks) ^ a_chunk: bit 0 of 2 ks is free
         for (int it = 0; it < n_iters; ++it) {
             const int s = it % STAGES;
             if (!mbar_wait(smem_u32(&full_bar[s]), (it / STAGES) & 1)) {
                 report_timeout(p.status, kKernelDecode, 2);
-                ok = false;
                 break;
             }
-            const uint32_t wb = w_base + s * W_STAGE_BYTES;
-            const uint32_t ab = a_base + s * A_STAGE_BYTES;
-            const uint4 x0 = lds128(wb + off_x0);
-            const uint4 y0 = lds128(wb + off_y0);
-            const uint4 x1 = lds128(wb + off_x1);
-            const uint4 y1 = lds128(wb + off_y1);
-            uint32_t a[4];
-            a[0] = lds32(ab + off_a0);
-            a[1] = lds32(ab + off_a0 + 8 * 128);
-            a[2] = lds32(ab + off_a2);
-            a[3] = lds32(ab + off_a2 + 8 * 128);
+            if (it == 0) TRACE(1);
+#ifdef B200Q_TRACE
+            if (p.skip_compute) { __syncwarp(); if (lane == 0) mbar_arrive(smem_u32(&empty_bar[s])); continue; }
+#endif
+            const uint32_t wb = w_base + s * W_STAGE_BYTES + off_w;
+            const uint32_t ab = a_base + s * A_STAGE_BYTES + off_a;
+            uint32_t q[4][4];
+            uint2 b[4][MT];
+#pragma unroll
+            for (int ks = 0; ks < 4; ++ks) {
+                ldmatrix_x2_trans_b8(q[ks], wb + ks * 2048);
+#pragma unroll
+                for (int mt = 0; mt < MT; ++mt) b[ks][mt] = lds64(ab + mt * 1024 + (((2 * ks) ^ a_chunk) << 4));
+            }
             __syncwarp();
-            if (lane == 0) mbar_arrive(smem_u32(&empty_bar[s]));  // stage is in registers now
-            uint32_t b_lo[16], b_hi[16];
-            rows_to_pairs(x0, y0, b_lo);
-            rows_to_pairs(x1, y1, b_hi);
+            if (lane == 0) mbar_arrive(smem_u32(&empty_bar[s]));  // the stage is in registers now
 #pragma unroll
-            for (int i = 0; i < 16; ++i) mma_m16n8k16(acc[i], a, b_lo[i], b_hi[i]);
-        }
-        (void)ok;
-    }
-
-    // ---------------- cross-warp reduction through shared memory ----------------
-    __syncthreads();  // every issued stage has landed and been consumed: the ring can be reused
-    float *red = reinterpret_cast<float *>(smem_gen);
-    if (warp < CONSUMER_WARPS) {
-        const int g = lane >> 2;
-        const int t = lane & 3;
-        float *mine = red + warp * BM * RED_STRIDE;
-        // MMA i holds columns {16 * j + i}; this thread has j = 2t, 2t+1 for rows g and g+8.  One
-        // word of skew per 32 columns keeps the 32 lanes on 32 banks.
+            for (int ks = 0; ks < 4; ++ks) {
 #pragma unroll
-        for (int i = 0; i < 16; ++i) {
-            const int c0 = 32 * t + i, c1 = c0 + 16;
-            mine[g * RED_STRIDE + c0 + (c0 >> 5)] = acc[i][0];
-            mine[g * RED_STRIDE + c1 + (c1 >> 5)] = acc[i][1];
-            mine[(g + 8) * RED_STRIDE + c0 + (c0 >> 5)] = acc[i][2];
-            mine[(g + 8) * RED_STRIDE + c1 + (c1 >> 5)] = acc[i][3];
+                for (int j = 0; j < 2; ++j) {
+                    // tile j: MMA rows g / g + 8 are columns 32 warp + 16 j + g / + 8 + g;
+                    // k slots (2t, 2t+1) and (2t+8, 2t+9) carry k = 4t, 4t+1 and 4t+2, 4t+3
+                    uint32_t a0, a1, a2, a3;
+                    cvt_s8x4_to_f16_pairs(q[ks][2 * j], a0, a2);
+                    cvt_s8x4_to_f16_pairs(q[ks][2 * j + 1], a1, a3);
+#pragma unroll
+                    for (int mt = 0; mt < MT; ++mt) mma_m16n8k16(acc[j][mt], a0, a1, a2, a3, b[ks][mt].x, b[ks][mt].y);
+                }
+            }
         }
     }
-    __syncthreads();
+    TRACE(2);
+    pdl_launch_dependents();  // the next kernel may start streaming its weight
 
-    const int col = threadIdx.x;          // column of the tile this thread finishes (threads 0..127)
-    const int n = n0 + col;
     int rows = p.M - m0;
     if (rows > BM) rows = BM;
-    const bool active = (col < BN) && (n < p.N);
-    const int skew = col + (col >> 5);
+    const bool consumer = warp < CONSUMER_WARPS;
+    // This thread's four columns inside the tile: 32 warp + 16 j + 8 h + g.
+    const int col_base = 32 * warp + g;
 
     if (p.mode == kModeDirect) {
-        if (active) {
-            const float sc = __half2float(p.scale[n]);
-            for (int r = 0; r < rows; ++r) {
-                float v = 0.0f;
+        cluster_wait_acquire();
+        if (consumer) {
 #pragma unroll
-                for (int w = 0; w < CONSUMER_WARPS; ++w) v += red[(w * BM + r) * RED_STRIDE + skew];
-                p.c[(size_t)(m0 + r) * p.N + n] = __float2half_rn(v * sc);
-            }
+            for (int j = 0; j < 2; ++j)
+#pragma unroll
+                for (int h = 0; h < 2; ++h) {
+                    const int nn = n0 + col_base + 16 * j + 8 * h;
+                    if (nn < p.N) {
+                        const float sc = __half2float(p.scale[nn]);
+#pragma unroll
+                        for (int mt = 0; mt < MT; ++mt)
+#pragma unroll
+                            for (int e = 0; e < 2; ++e) {
+                                const int r = 8 * mt + 2 * t + e;
+                                if (r < rows) p.c[(size_t)(m0 + r) * p.N + nn] = __float2half_rn(acc[j][mt][2 * h + e] * sc);
+                            }
+                    }
+                }
         }
         return;
     }
 
-    if (p.mode == kModeCluster) {
-        // ---------------- split-K inside a cluster: partial tiles meet through distributed shared memory ----------------
-        // The CTAs of a cluster are the `splits` CTAs of one output tile.  Each first folds its four
-        // warp slabs into slab 0, then CTA `rank` sums columns [rank * BN / splits, ...) over all CTAs
-        // in rank order (a fixed order: the result does not depend on timing).
-        cg::cluster_group cluster = cg::this_cluster();
-        if (col < BN) {
-            for (int r = 0; r < rows; ++r) {
-                float v = 0.0f;
+    // ---------------- split-K ----------------
+    // Level 1, inside a cluster: every CTA stores its partial tile into the shared memory of the CTA
+    // that owns those columns; one cluster barrier later the owner holds the partials of all ranks.
+    // (Without a cluster the CTA is its own owner and the same code runs on local shared memory.)
+    const uint32_t nranks = cluster_nctarank();
+    const uint32_t rank = cluster_ctarank();
+    const int cols_per = BN / (int)nranks;  // 128 ... 16 columns per owner
+    cluster_wait_acquire();                 // every CTA of the cluster is running
+    if (consumer) {
 #pragma unroll
-                for (int w = 0; w < CONSUMER_WARPS; ++w) v += red[(w * BM + r) * RED_STRIDE + skew];
-                red[r * RED_STRIDE + skew] = v;
+        for (int j = 0; j < 2; ++j)
+#pragma unroll
+            for (int h = 0; h < 2; ++h) {
+                const int col = col_base + 16 * j + 8 * h;
+                const uint32_t owner = (uint32_t)(col / cols_per);
+                const int col_in = col - (int)owner * cols_per;
+                const uint32_t remote = map_to_rank(recv_base, owner);
+#pragma unroll
+                for (int mt = 0; mt < MT; ++mt)
+#pragma unroll
+                    for (int e = 0; e < 2; ++e) {
+                        const int r = 8 * mt + 2 * t + e;
+                        if (r < rows) st_cluster_f32(remote + (((int)rank * BM + r) * cols_per + col_in) * 4, acc[j][mt][2 * h + e]);
+                    }
             }
-        }
-        cluster.sync();
-        const unsigned int csize = cluster.num_blocks();
-        const unsigned int rank = cluster.block_rank();
-        const int cols_per = BN / (int)csize;
+    }
+    cluster_arrive_release();
+    cluster_wait_acquire();  // all partial tiles of this CTA's columns have landed
+    TRACE(3);
+    const int col_first = n0 + (int)rank * cols_per;  // first column this CTA owns
+    if (p.groups == 1) {
         for (int idx = threadIdx.x; idx < rows * cols_per; idx += THREADS) {
             const int r = idx / cols_per;
-            const int cc = (int)rank * cols_per + (idx - r * cols_per);
-            const int nn = n0 + cc;
+            const int cc = idx - r * cols_per;
+            const int nn = col_first + cc;
             if (nn < p.N) {
-                const int off = r * RED_STRIDE + cc + (cc >> 5);
                 float v = 0.0f;
-                for (unsigned int j = 0; j < csize; ++j) v += cluster.map_shared_rank(red, j)[off];
+                for (uint32_t jr = 0; jr < nranks; ++jr) v += recv[((int)jr * BM + r) * cols_per + cc];
                 p.c[(size_t)(m0 + r) * p.N + nn] = __float2half_rn(v * __half2float(p.scale[nn]));
             }
         }
-        cluster.sync();  // nobody leaves while a peer may still read its shared memory
+        TRACE(4);
         return;
     }
 
-    // ---------------- split-K through the workspace: publish the partial tile, last CTA of the tile finishes ----------------
-    if (active) {
-        for (int r = 0; r < rows; ++r) {
+    // Level 2, across the `groups` clusters of a tile: each owner publishes its cluster's sum in the
+    // caller's workspace; the last of the `groups` owners of a column slice to arrive adds them in
+    // group order and finishes.
+    const int group = (int)(blockIdx.y / nranks);
+    for (int idx = threadIdx.x; idx < rows * cols_per; idx += THREADS) {
+        const int r = idx / cols_per;
+        const int cc = idx - r * cols_per;
+        const int nn = col_first + cc;
+        if (nn < p.N) {
             float v = 0.0f;
-#pragma unroll
-            for (int w = 0; w < CONSUMER_WARPS; ++w) v += red[(w * BM + r) * RED_STRIDE + skew];
-            p.partial[((size_t)split * p.M + (m0 + r)) * p.N + n] = v;
+            for (uint32_t jr = 0; jr < nranks; ++jr) v += recv[((int)jr * BM + r) * cols_per + cc];
+            __stcg(&p.partial[((size_t)group * p.M + (m0 + r)) * p.N + nn], v);
         }
     }
     __threadfence();
     __syncthreads();
-    const unsigned int tile_id = blockIdx.z * gridDim.x + blockIdx.x;
+    const unsigned int slot = (blockIdx.z * gridDim.x + blockIdx.x) * nranks + rank;
     if (threadIdx.x == 0) {
-        const unsigned int prev = atomicAdd(&p.counters[tile_id], 1u);
-        is_last = (prev == (unsigned int)(p.splits - 1)) ? 1u : 0u;
+        const unsigned int prev = atomicAdd(&p.counters[slot], 1u);
+        is_last = (prev == (unsigned int)(p.groups - 1)) ? 1u : 0u;
     }
     __syncthreads();
     if (is_last == 0) return;
     __threadfence();
-    if (active) {
-        const float sc = __half2float(p.scale[n]);
-        for (int r = 0; r < rows; ++r) {
+    for (int idx = threadIdx.x; idx < rows * cols_per; idx += THREADS) {
+        const int r = idx / cols_per;
+        const int cc = idx - r * cols_per;
+        const int nn = col_first + cc;
+        if (nn < p.N) {
             float v = 0.0f;
 #pragma unroll 4
-            for (int s = 0; s < p.splits; ++s) v += __ldcg(&p.partial[((size_t)s * p.M + (m0 + r)) * p.N + n]);
-            p.c[(size_t)(m0 + r) * p.N + n] = __float2half_rn(v * sc);
+            for (int gr = 0; gr < p.groups; ++gr) v += __ldcg(&p.partial[((size_t)gr * p.M + (m0 + r)) * p.N + nn]);
+            p.c[(size_t)(m0 + r) * p.N + nn] = __float2half_rn(v * __half2float(p.scale[nn]));
         }
     }
-    if (threadIdx.x == 0) p.counters[tile_id] = 0;  // leave the workspace ready for the next call
+    if (threadIdx.x == 0) p.counters[slot] = 0;  // leave the workspace ready for the next call
 }
 
 }  // namespace decode
@@ -307,36 +401,28 @@ DecodePlan plan_decode(int64_t M, int64_t N, int64_t K) {
     const int k_iters = (int)ceil_div(K, BK);
     int sms = sm_count();
     if (sms <= 0) sms = 148;
-    const int64_t target = (int64_t)sms * 3;  // three CTAs of this kernel share an SM
+    const int64_t target = (int64_t)sms * kCtasPerSm;
     const int64_t tiles = (int64_t)pl.n_tiles * pl.m_tiles;
+    // CTAs per tile that fill the machine once, each with at least eight 64-row steps of work.
     int64_t splits = tiles > 0 ? target / tiles : 1;
-    const int max_splits = k_iters / 4 > 0 ? k_iters / 4 : 1;  // at least four stages of work per CTA
+    const int max_splits = k_iters / 8 > 0 ? k_iters / 8 : 1;
     if (splits > max_splits) splits = max_splits;
     if (splits > 64) splits = 64;
     if (splits < 1) splits = 1;
-    if (splits <= 2 * kMaxCluster) {
-        // Up to a cluster's worth (and a little beyond: a full cluster beats a few more CTAs that need
-        // the workspace): the splits of a tile form a cluster and meet in distributed shared memory.
-        int c = 1;
-        while (c * 2 <= splits && c * 2 <= kMaxCluster) c *= 2;
-        splits = c;
-        pl.cluster = c;
-    } else {
-        pl.cluster = 1;
-        if (tiles > kMaxCounters) splits = 1;
-    }
-    pl.iters_per_split = (int)ceil_div(k_iters, splits);
-    if (pl.cluster > 1) {
-        pl.splits = pl.cluster;  // the grid must hold whole clusters; a split may have fewer steps, or none
-    } else {
-        pl.splits = (int)ceil_div(k_iters, pl.iters_per_split);
-        if (pl.splits < 1) pl.splits = 1;
-    }
-    const bool workspace = pl.cluster == 1 && pl.splits > 1;
+    // The splits of a tile form clusters (partials meet in distributed shared memory); more splits
+    // than a cluster holds become several clusters per tile that meet in the workspace.
+    int c = 1;
+    while (c * 2 <= splits && c * 2 <= kMaxCluster) c *= 2;
+    int groups = (int)(splits / c);
+    if (groups < 1 || tiles * c > kMaxCounters) groups = 1;
+    pl.cluster = c;
+    pl.groups = groups;
+    pl.splits = c * groups;  // the grid holds whole clusters; a split may get fewer steps than others, or none
+    pl.iters_per_split = (int)ceil_div(k_iters, pl.splits);
     // The counter region has one fixed size, so that counters never land on bytes an earlier call of
     // another shape used for partial sums: the region stays all-zero between calls.
-    pl.counter_bytes = workspace ? (size_t)kMaxCounters * 4 : 0;
-    pl.partial_bytes = workspace ? (size_t)pl.splits * M * N * 4 : 0;
+    pl.counter_bytes = groups > 1 ? (size_t)kMaxCounters * 4 : 0;
+    pl.partial_bytes = groups > 1 ? (size_t)groups * M * N * 4 : 0;
     return pl;
 }
 
@@ -354,6 +440,7 @@ int launch_decode_kn(const void *a, const void *wq, const void *scale, void *c, 
         pl.iters_per_split = (int)ceil_div(k_end - k_begin, BK);
         pl.splits = 1;
         pl.cluster = 1;
+        pl.groups = 1;
         pl.partial_bytes = 0;
         pl.counter_bytes = 0;
     }
@@ -382,14 +469,22 @@ int launch_decode_kn(const void *a, const void *wq, const void *scale, void *c, 
     p.k_begin = (int)k_begin;
     p.k_end = (int)k_end;
     p.iters_per_split = pl.iters_per_split;
-    p.splits = pl.splits;
-    p.mode = pl.splits == 1 ? kModeDirect : (pl.cluster > 1 ? kModeCluster : kModeWorkspace);
+    p.groups = pl.groups;
+    p.mode = pl.splits == 1 ? kModeDirect : kModeSplit;
+#ifdef B200Q_TRACE
+    p.trace = g_trace;
+    p.skip_compute = getenv("B200Q_SKIP") ? atoi(getenv("B200Q_SKIP")) : 0;
+#endif
 
+    auto kernel = (M - (int64_t)(pl.m_tiles - 1) * BM <= 8 && pl.m_tiles == 1) ? qlinear_decode_kn_kernel<1> : qlinear_decode_kn_kernel<2>;
     static bool attr_set[64] = {false};  // per device; a repeated set is harmless
     int dev = 0;
     B200Q_CUDA_TRY(cudaGetDevice(&dev));
     if (dev < 0 || dev >= 64 || !attr_set[dev]) {
-        B200Q_CUDA_TRY(cudaFuncSetAttribute(qlinear_decode_kn_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
+        B200Q_CUDA_TRY(cudaFuncSetAttribute(qlinear_decode_kn_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
+        B200Q_CUDA_TRY(cudaFuncSetAttribute(qlinear_decode_kn_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
+        B200Q_CUDA_TRY(cudaFuncSetAttribute(qlinear_decode_kn_kernel<1>, cudaFuncAttributeNonPortableClusterSizeAllowed, 1));
+        B200Q_CUDA_TRY(cudaFuncSetAttribute(qlinear_decode_kn_kernel<2>, cudaFuncAttributeNonPortableClusterSizeAllowed, 1));
         if (dev >= 0 && dev < 64) attr_set[dev] = true;
     }
     cudaLaunchConfig_t cfg = {};
@@ -397,14 +492,16 @@ int launch_decode_kn(const void *a, const void *wq, const void *scale, void *c, 
     cfg.blockDim = dim3(THREADS, 1, 1);
     cfg.dynamicSmemBytes = SMEM_BYTES;
     cfg.stream = stream;
-    cudaLaunchAttribute attrs[1];
+    cudaLaunchAttribute attrs[2];
     attrs[0].id = cudaLaunchAttributeClusterDimension;
     attrs[0].val.clusterDim.x = 1;
     attrs[0].val.clusterDim.y = (unsigned)pl.cluster;
     attrs[0].val.clusterDim.z = 1;
+    attrs[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attrs[1].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attrs;
-    cfg.numAttrs = 1;
-    B200Q_CUDA_TRY(cudaLaunchKernelEx(&cfg, qlinear_decode_kn_kernel, map_w, map_a, p));
+    cfg.numAttrs = 2;
+    B200Q_CUDA_TRY(cudaLaunchKernelEx(&cfg, kernel, map_w, map_a, p));
     return B200Q_OK;
 }
 

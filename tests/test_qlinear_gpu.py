@@ -40,7 +40,8 @@ def _check(a_np, wq_np, scale_np, c_gpu, layout='KN', k_begin=0, k_end=None):
 # decode shapes of the benchmark (M in {1, 4, 16}, K = 4096, N in {4096, 11008}) and the reference's own
 # test shapes (tests/operators_core/test_quantization.py:39-47)
 @pytest.mark.parametrize('m,k,n', [(1, 4096, 4096), (4, 4096, 4096), (16, 4096, 4096), (1, 4096, 11008), (16, 4096, 11008),
-                                   (16, 11008, 4096), (3, 512, 256), (7, 1024, 384), (16, 64, 128), (1, 8, 16), (5, 200, 48)])
+                                   (16, 11008, 4096), (3, 512, 256), (7, 1024, 384), (16, 64, 128), (1, 8, 16), (5, 200, 48),
+                                   (8, 8192, 3584), (9, 16384, 256), (2, 28672, 1024), (12, 2048, 16), (16, 8192, 1024)])
 def test_qlinear_small_m(m, k, n):
     wq, scale = _quantized(k, n, seed=m + k)
     a = seeded_activation(m, k, seed=n)
@@ -184,11 +185,14 @@ def test_qlinear_argument_checks_follow_the_reference():
         hidet_b200.symmetric_quant_matmul_f16_i8(a, wq, scale, 1.5)
     # a too small workspace is reported, not overrun
     with pytest.raises(ffi.BackendException, match='workspace'):
-        big_a = torch.zeros(16, 4096, dtype=torch.float16, device='cuda')
-        big_w = torch.zeros(4096, 4096, dtype=torch.int8, device='cuda')
-        big_s = torch.ones(4096, dtype=torch.float16, device='cuda')
-        out = torch.empty(16, 4096, dtype=torch.float16, device='cuda')
+        # a narrow, deep problem is split over more CTAs than a cluster holds and needs the workspace
+        m, n, k = 4, 256, 16384
+        assert ffi.func('b200q_qlinear_workspace_bytes')(m, n, k, 0) > 256
+        big_a = torch.zeros(m, k, dtype=torch.float16, device='cuda')
+        big_w = torch.zeros(k, n, dtype=torch.int8, device='cuda')
+        big_s = torch.ones(n, dtype=torch.float16, device='cuda')
+        out = torch.empty(m, n, dtype=torch.float16, device='cuda')
         tiny = torch.zeros(256, dtype=torch.uint8, device='cuda')
-        ffi.func('b200q_qlinear_f16_i8')(big_a.data_ptr(), big_w.data_ptr(), big_s.data_ptr(), out.data_ptr(), 16, 4096, 4096, 0,
+        ffi.func('b200q_qlinear_f16_i8')(big_a.data_ptr(), big_w.data_ptr(), big_s.data_ptr(), out.data_ptr(), m, n, k, 0,
                                          tiny.data_ptr(), tiny.numel(), torch.cuda.current_stream().cuda_stream)
     assert ffi.func('b200q_check_status')() == ffi.OK
