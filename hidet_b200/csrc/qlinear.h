@@ -29,4 +29,13 @@ int launch_decode_kn(const void *a, const void *wq, const void *scale, void *c, 
                      int64_t k_begin, int64_t k_end, bool allow_split, void *workspace, size_t workspace_bytes,
                      cudaStream_t stream);
 
+// The tensor-memory kernel for large M: same operand requirements as the small-M kernel.
+bool prefill_kn_supported(const void *a, const void *wq, int64_t N, int64_t K);
+int launch_prefill_kn(const void *a, const void *wq, const void *scale, void *c, int64_t M, int64_t N, int64_t K,
+                      cudaStream_t stream);
+
+// Smallest M served by the tensor-memory kernel.  Its tile spans 256 activation rows, so below this
+// the small-M kernel, which re-streams the weight once per 16 rows, is still the faster one.
+constexpr int64_t kPrefillMinM = 33;
+
 }  // namespace b200q

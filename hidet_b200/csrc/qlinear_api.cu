@@ -76,6 +76,9 @@ B200Q_API int b200q_qlinear_f16_i8(const void *a, const void *wq, const void *sc
         B200Q_CUDA_TRY(cudaMemsetAsync(c, 0, (size_t)M * N * sizeof(__half), s));
         return B200Q_OK;
     }
+    if (w_layout == B200Q_LAYOUT_KN && M >= kPrefillMinM && prefill_kn_supported(a, wq, N, K)) {
+        return launch_prefill_kn(a, wq, scale, c, M, N, K, s);
+    }
     if (w_layout == B200Q_LAYOUT_KN && decode_kn_supported(a, wq, N, K)) {
         return launch_decode_kn(a, wq, scale, c, M, N, K, 0, K, true, workspace, workspace_bytes, s);
     }

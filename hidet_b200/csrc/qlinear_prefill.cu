@@ -1,0 +1,368 @@
+// Large-M (prefill) f16 x int8 quantized linear for weights in the reference's [K, N] layout, on the
+// fifth-generation tensor cores: tcgen05.mma with fp32 accumulators in tensor memory.
+//
+// The product is computed transposed, D[n, m] = sum_k W[k, n] * A[m, k], so that the operand that needs
+// work before the MMA -- the int8 weight -- is the 128-row operand and the activations, which TMA can
+// deliver in final form, are the 256-column operand: per 128 x 256 x 16 MMA the tensor core reads
+// 4 KB + 8 KB of shared memory, the converters read 2 KB and write 4 KB, which leaves shared-memory
+// bandwidth headroom that the opposite assignment would not.
+//
+// One persistent CTA per SM, ten warps:
+//   warp 8      TMA producer: per 64-k stage one int8 tile [64 k][128 n] (plain layout) and one
+//               activation tile [256 m][64 k] f16 (128B swizzle = K-major MMA operand as is)
+//   warps 4-7   converters: int8 -> exact f16 in registers, written as the MN-major, 128B-swizzled MMA
+//               operand ([2 column blocks][8 k-groups][8 k][64 n]), then a proxy fence and an mbarrier
+//   warp 9      MMA issuer (one lane): four K=16 MMAs per stage into one of two 256-column TMEM
+//               accumulators; tcgen05.commit frees the stage / publishes the accumulator
+//   warps 0-3   epilogue: tcgen05.ld of the accumulator (lane = weight column n, column = row m),
+//               times scale[n], one rounding to f16, stores to C[m, n]; overlaps the next tile's MMAs
+// Rows beyond M, columns beyond N and k beyond K are zero-filled by TMA and never stored.
+//
+// Every wait is bounded: a wait that runs out records where in the device status word, the role
+// leaves its loops, and the CTA still releases its tensor memory and returns.
+//
+// Replaces, for large M, the generated mma.sync kernel of
+// python/hidet/graph/ops/quant/matmul_f16_i8.py:136-485 (f16 accumulation) and the separate sum over
+// split-K parts that follows it (python/hidet/graph/ops/quant/resolve.py:99).
+#include "common.cuh"
+#include "qlinear.h"
+
+namespace b200q {
+namespace prefill {
+
+constexpr int TN = 128;                     // weight columns per tile = MMA M
+constexpr int TM = 256;                     // activation rows per tile = MMA N
+constexpr int BK = 64;                      // k per stage = four MMAs of K = 16
+constexpr int STAGES = 4;
+constexpr int RAW_BYTES = BK * TN;          // int8 tile
+constexpr int WF_BYTES = BK * TN * 2;       // converted f16 tile
+constexpr int ACT_BYTES = TM * BK * 2;      // activation tile
+constexpr int STAGE_BYTES = RAW_BYTES + WF_BYTES + ACT_BYTES;
+constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024;  // + alignment slack
+constexpr int THREADS = 320;
+constexpr int EPI_WARP0 = 0, CONV_WARP0 = 4, PRODUCER_WARP = 8, MMA_WARP = 9;
+constexpr uint32_t TMEM_COLS = 512;         // two accumulators of TM fp32 columns
+
+// tcgen05 instruction descriptor, kind::f16: D = f32, A = B = f16, A is MN-major, B is K-major,
+// N = 256 (bits 17..22 hold N / 8), M = 128 (bits 24..28 hold M / 16).
+constexpr uint32_t kInstrDesc = (1u << 4) | (1u << 15) | ((uint32_t)(TM >> 3) << 17) | ((uint32_t)(TN >> 4) << 24);
+
+// Shared-memory matrix descriptor: start address, leading / stride byte offsets (all in 16-byte
+// units), descriptor version 1, 128-byte swizzle.
+__device__ __forceinline__ uint64_t smem_desc(uint32_t addr, uint32_t leading_bytes, uint32_t stride_bytes) {
+    return (uint64_t)((addr >> 4) & 0x3fffu) | ((uint64_t)((leading_bytes >> 4) & 0x3fffu) << 16) |
+           ((uint64_t)((stride_bytes >> 4) & 0x3fffu) << 32) | (1ull << 46) | (2ull << 61);
+}
+
+__device__ __forceinline__ void tmem_alloc(uint32_t smem_dst, uint32_t cols) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_dst), "r"(cols) : "memory");
+}
+__device__ __forceinline__ void tmem_relinquish() {
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t cols) {
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(cols) : "memory");
+}
+__device__ __forceinline__ void tc_fence_before_sync() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after_sync() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+
+// D[tmem] (+)= A[smem] * B[smem]; accumulate == 0 overwrites D.
+__device__ __forceinline__ void umma_f16(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t"
+        ".reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t"
+        "}\n"
+        ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+// The mbarrier gets one arrival when every MMA issued so far by this thread has completed.
+__device__ __forceinline__ void umma_commit(uint32_t bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+// 32 consecutive fp32 columns of this warp's 32 TMEM lanes: thread i gets lane (base lane + i).
+__device__ __forceinline__ void tmem_ld_32x32(uint32_t taddr, uint32_t (&v)[32]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+        : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]), "=r"(v[8]), "=r"(v[9]),
+          "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15]), "=r"(v[16]), "=r"(v[17]), "=r"(v[18]),
+          "=r"(v[19]), "=r"(v[20]), "=r"(v[21]), "=r"(v[22]), "=r"(v[23]), "=r"(v[24]), "=r"(v[25]), "=r"(v[26]), "=r"(v[27]),
+          "=r"(v[28]), "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
+        : "r"(taddr)
+        : "memory");
+}
+__device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+
+__device__ __forceinline__ uint4 lds128(uint32_t addr) {
+    uint4 v;
+    asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr));
+    return v;
+}
+__device__ __forceinline__ void sts128(uint32_t addr, uint32_t a, uint32_t b, uint32_t c, uint32_t d) {
+    asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(a), "r"(b), "r"(c), "r"(d) : "memory");
+}
+
+// Four signed bytes (b0 .. b3) -> f16 pairs (b0, b1) and (b2, b3), exactly (0x6400 | u is 1024 + u).
+__device__ __forceinline__ void cvt_s8x4_to_f16_pairs(uint32_t v, uint32_t &p01, uint32_t &p23) {
+    const uint32_t u = v ^ 0x80808080u;
+    const uint32_t e01 = __byte_perm(u, 0x64646464u, 0x4140);
+    const uint32_t e23 = __byte_perm(u, 0x64646464u, 0x4342);
+    const uint32_t bias = 0x64806480u;
+    asm("sub.f16x2 %0, %1, %2;" : "=r"(p01) : "r"(e01), "r"(bias));
+    asm("sub.f16x2 %0, %1, %2;" : "=r"(p23) : "r"(e23), "r"(bias));
+}
+
+struct Params {
+    const __half *scale;
+    __half *c;
+    unsigned int *status;
+    int M, N, K;
+    int n_tiles, m_tiles;
+};
+
+__global__ void __launch_bounds__(THREADS, 1) qlinear_prefill_kn_kernel(const __grid_constant__ CUtensorMap map_w,
+                                                                        const __grid_constant__ CUtensorMap map_a,
+                                                                        const Params p) {
+    extern __shared__ unsigned char smem_dyn[];
+    __shared__ __align__(8) uint64_t tma_full[STAGES];   // TMA bytes of a stage have landed
+    __shared__ __align__(8) uint64_t conv_full[STAGES];  // the four converter warps have written the f16 tile
+    __shared__ __align__(8) uint64_t slot_free[STAGES];  // the MMAs that read the stage have completed
+    __shared__ __align__(8) uint64_t acc_full[2];        // an accumulator holds a finished tile
+    __shared__ __align__(8) uint64_t acc_empty[2];       // the four epilogue warps have read it out
+    __shared__ uint32_t tmem_base_slot;
+
+    const uint32_t smem_base = (smem_u32(smem_dyn) + 1023u) & ~1023u;  // swizzled operands need 1024-byte alignment
+    const int warp = threadIdx.x >> 5;
+    const int lane = threadIdx.x & 31;
+    const int total_tiles = p.n_tiles * p.m_tiles;
+    const int k_blocks = (p.K + BK - 1) / BK;
+
+    // stage layout: [activations 32 KB][f16 weights 16 KB][int8 weights 8 KB]
+    auto act_addr = [&](int s) { return smem_base + s * STAGE_BYTES; };
+    auto wf_addr = [&](int s) { return smem_base + s * STAGE_BYTES + ACT_BYTES; };
+    auto raw_addr = [&](int s) { return smem_base + s * STAGE_BYTES + ACT_BYTES + WF_BYTES; };
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < STAGES; ++s) {
+            mbar_init(smem_u32(&tma_full[s]), 1);
+            mbar_init(smem_u32(&conv_full[s]), 4);
+            mbar_init(smem_u32(&slot_free[s]), 1);
+        }
+        for (int b = 0; b < 2; ++b) {
+            mbar_init(smem_u32(&acc_full[b]), 1);
+            mbar_init(smem_u32(&acc_empty[b]), 4);
+        }
+        mbar_fence_init();
+    }
+    if (warp == MMA_WARP) {
+        tmem_alloc(smem_u32(&tmem_base_slot), TMEM_COLS);
+        tmem_relinquish();
+    }
+    tc_fence_before_sync();
+    __syncthreads();
+    tc_fence_after_sync();
+    const uint32_t tmem_base = tmem_base_slot;
+
+    if (warp == PRODUCER_WARP) {
+        // ---------------- TMA producer ----------------
+        if (lane == 0) {
+            tma_prefetch_desc(&map_w);
+            tma_prefetch_desc(&map_a);
+            const uint64_t keep = l2_policy_evict_last();  // both operands are re-read by other tiles: keep them in L2
+            uint32_t i = 0;
+            bool ok = true;
+            for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
+                const int n0 = (tile % p.n_tiles) * TN;
+                const int m0 = (tile / p.n_tiles) * TM;
+                for (int kb = 0; kb < k_blocks; ++kb, ++i) {
+                    const int s = i % STAGES;
+                    const uint32_t use = i / STAGES;
+                    if (use >= 1 && !mbar_wait(smem_u32(&slot_free[s]), (use - 1) & 1)) {
+                        report_timeout(p.status, kKernelPrefill, 1);
+                        ok = false;
+                        break;
+                    }
+                    const uint32_t bar = smem_u32(&tma_full[s]);
+                    mbar_expect_tx(bar, RAW_BYTES + ACT_BYTES);
+                    tma_load_2d_hint(raw_addr(s), &map_w, n0, kb * BK, bar, keep);
+                    tma_load_2d_hint(act_addr(s), &map_a, kb * BK, m0, bar, keep);
+                }
+            }
+        }
+    } else if (warp == MMA_WARP) {
+        // ---------------- MMA issuer ----------------
+        if (lane == 0) {
+            uint32_t i = 0, t_iter = 0;
+            bool ok = true;
+            for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, ++t_iter) {
+                const uint32_t buf = t_iter & 1, acc_use = t_iter >> 1;
+                if (acc_use >= 1 && !mbar_wait(smem_u32(&acc_empty[buf]), (acc_use - 1) & 1)) {
+                    report_timeout(p.status, kKernelPrefill, 2);
+                    break;
+                }
+                tc_fence_after_sync();
+                const uint32_t d_addr = tmem_base + buf * TM;
+                for (int kb = 0; kb < k_blocks; ++kb, ++i) {
+                    const int s = i % STAGES;
+                    const uint32_t use = i / STAGES;
+                    if (!mbar_wait(smem_u32(&tma_full[s]), use & 1) || !mbar_wait(smem_u32(&conv_full[s]), use & 1)) {
+                        report_timeout(p.status, kKernelPrefill, 3);
+                        ok = false;
+                        break;
+                    }
+                    tc_fence_after_sync();
+#pragma unroll
+                    for (int ks = 0; ks < BK / 16; ++ks) {
+                        // A: MN-major f16 weights, column blocks 8192 B apart, 8-k groups 1024 B apart; K = 16 is two groups.
+                        const uint64_t da = smem_desc(wf_addr(s) + ks * 2048, 8192, 1024);
+                        // B: K-major activations, 8-row groups 1024 B apart; K = 16 is 32 bytes along the swizzled row.
+                        const uint64_t db = smem_desc(act_addr(s) + ks * 32, 16, 1024);
+                        umma_f16(d_addr, da, db, kInstrDesc, (kb > 0 || ks > 0) ? 1u : 0u);
+                    }
+                    umma_commit(smem_u32(&slot_free[s]));
+                }
+                if (ok) umma_commit(smem_u32(&acc_full[buf]));
+            }
+        }
+    } else if (warp >= CONV_WARP0 && warp < CONV_WARP0 + 4) {
+        // ---------------- converters ----------------
+        const int ct = threadIdx.x - CONV_WARP0 * 32;  // 0..127
+        const int ci = ct & 7;                         // 16-byte chunk of an int8 row: columns 16 ci .. 16 ci + 15
+        const int rb = ct >> 3;                        // row inside a pass of 16 rows
+        // f16 chunks (8 columns each) 2 ci and 2 ci + 1 of the 16 per row; chunk c lives in column block
+        // c / 8 at slot (c % 8) ^ (k % 8) of its 128-byte row.  Half of the threads write the odd chunk
+        // first so that the eight threads of a row hit eight different bank groups.
+        const int c_first = (ci & 4) ? 2 * ci + 1 : 2 * ci;
+        const int c_second = (ci & 4) ? 2 * ci : 2 * ci + 1;
+        uint32_t i = 0;
+        bool ok = true;
+        for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
+            for (int kb = 0; kb < k_blocks; ++kb, ++i) {
+                const int s = i % STAGES;
+                const uint32_t use = i / STAGES;
+                if (!mbar_wait(smem_u32(&tma_full[s]), use & 1)) {
+                    report_timeout(p.status, kKernelPrefill, 4);
+                    ok = false;
+                    break;
+                }
+                const uint32_t raw = raw_addr(s), wf = wf_addr(s);
+#pragma unroll
+                for (int pass = 0; pass < BK / 16; ++pass) {
+                    const int k = pass * 16 + rb;
+                    const uint4 v = lds128(raw + k * 128 + ci * 16);
+                    uint32_t h[8];
+                    cvt_s8x4_to_f16_pairs(v.x, h[0], h[1]);
+                    cvt_s8x4_to_f16_pairs(v.y, h[2], h[3]);
+                    cvt_s8x4_to_f16_pairs(v.z, h[4], h[5]);
+                    cvt_s8x4_to_f16_pairs(v.w, h[6], h[7]);
+                    const uint32_t row = wf + (k >> 3) * 1024 + (k & 7) * 128;
+                    const uint32_t a_first = row + (c_first >> 3) * 8192 + (((c_first & 7) ^ (k & 7)) << 4);
+                    const uint32_t a_second = row + (c_second >> 3) * 8192 + (((c_second & 7) ^ (k & 7)) << 4);
+                    if (ci & 4) {
+                        sts128(a_first, h[4], h[5], h[6], h[7]);
+                        sts128(a_second, h[0], h[1], h[2], h[3]);
+                    } else {
+                        sts128(a_first, h[0], h[1], h[2], h[3]);
+                        sts128(a_second, h[4], h[5], h[6], h[7]);
+                    }
+                }
+                fence_proxy_async_smem();  // the tensor core reads these bytes through the async proxy
+                __syncwarp();
+                if (lane == 0) mbar_arrive(smem_u32(&conv_full[s]));
+            }
+        }
+    } else if (warp < 4) {
+        // ---------------- epilogue ----------------
+        const int q = warp;  // TMEM lanes 32 q .. 32 q + 31
+        uint32_t t_iter = 0;
+        for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x, ++t_iter) {
+            const int n0 = (tile % p.n_tiles) * TN;
+            const int m0 = (tile / p.n_tiles) * TM;
+            const uint32_t buf = t_iter & 1, acc_use = t_iter >> 1;
+            if (!mbar_wait(smem_u32(&acc_full[buf]), acc_use & 1)) {
+                report_timeout(p.status, kKernelPrefill, 5);
+                break;
+            }
+            tc_fence_after_sync();
+            const int n = n0 + 32 * q + lane;
+            const bool n_ok = n < p.N;
+            const float sc = n_ok ? __half2float(p.scale[n]) : 0.0f;
+            __half *dst = p.c + (size_t)m0 * p.N + n;
+            const int m_left = p.M - m0;
+#pragma unroll 1
+            for (int cb = 0; cb < TM / 32; ++cb) {
+                uint32_t v[32];
+                tmem_ld_32x32(tmem_base + ((uint32_t)(32 * q) << 16) + buf * TM + cb * 32, v);
+                tmem_ld_wait();
+                if (n_ok) {
+#pragma unroll
+                    for (int j = 0; j < 32; ++j) {
+                        const int m = cb * 32 + j;
+                        if (m < m_left) dst[(size_t)m * p.N] = __float2half_rn(__uint_as_float(v[j]) * sc);
+                    }
+                }
+            }
+            tc_fence_before_sync();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(smem_u32(&acc_empty[buf]));
+        }
+    }
+
+    // ---------------- teardown: everyone is done with tensor memory ----------------
+    tc_fence_before_sync();
+    __syncthreads();
+    if (warp == MMA_WARP) {
+        tc_fence_after_sync();
+        tmem_dealloc(tmem_base, TMEM_COLS);
+    }
+}
+
+}  // namespace prefill
+
+bool prefill_kn_supported(const void *a, const void *wq, int64_t N, int64_t K) {
+    return (N % 16 == 0) && (K % 8 == 0) && ((reinterpret_cast<uintptr_t>(a) & 15u) == 0) &&
+           ((reinterpret_cast<uintptr_t>(wq) & 15u) == 0);
+}
+
+int launch_prefill_kn(const void *a, const void *wq, const void *scale, void *c, int64_t M, int64_t N, int64_t K,
+                      cudaStream_t stream) {
+    using namespace prefill;
+    CUtensorMap map_w, map_a;
+    int rc = make_tensor_map_2d(&map_w, CU_TENSOR_MAP_DATA_TYPE_UINT8, wq, (uint64_t)N, (uint64_t)K, (uint64_t)N, TN, BK,
+                                CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B);
+    if (rc != B200Q_OK) return rc;
+    rc = make_tensor_map_2d(&map_a, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, a, (uint64_t)K, (uint64_t)M, (uint64_t)K * 2, BK, TM,
+                            CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B);
+    if (rc != B200Q_OK) return rc;
+
+    Params p;
+    p.scale = static_cast<const __half *>(scale);
+    p.c = static_cast<__half *>(c);
+    p.status = device_status_word();
+    p.M = (int)M;
+    p.N = (int)N;
+    p.K = (int)K;
+    p.n_tiles = (int)ceil_div(N, TN);
+    p.m_tiles = (int)ceil_div(M, TM);
+    const int64_t total = (int64_t)p.n_tiles * p.m_tiles;
+    if (total > 2147483647LL) return set_error(B200Q_UNSUPPORTED, "qlinear: problem too large for the tile counter");
+    int sms = sm_count();
+    if (sms <= 0) sms = 148;
+    const unsigned grid = (unsigned)(total < sms ? total : sms);
+
+    static bool attr_set[64] = {false};  // per device; a repeated set is harmless
+    int dev = 0;
+    B200Q_CUDA_TRY(cudaGetDevice(&dev));
+    if (dev < 0 || dev >= 64 || !attr_set[dev]) {
+        B200Q_CUDA_TRY(cudaFuncSetAttribute(qlinear_prefill_kn_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
+        if (dev >= 0 && dev < 64) attr_set[dev] = true;
+    }
+    qlinear_prefill_kn_kernel<<<grid, THREADS, SMEM_BYTES, stream>>>(map_w, map_a, p);
+    B200Q_CHECK_LAUNCH("qlinear_prefill_kn_kernel");
+    return B200Q_OK;
+}
+
+}  // namespace b200q
