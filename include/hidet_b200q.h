@@ -124,6 +124,36 @@ B200Q_API int b200q_qlinear_f16_i8_parts(const void *a, const void *wq, const vo
                                          int64_t N, int64_t K, int k_parts, void *stream);
 
 /*
+ * Bytes of the scratch array built into the library for b200q_qlinear_f16_i8_static (512 KiB).
+ * No counterpart in the reference.
+ */
+B200Q_API size_t b200q_qlinear_static_scratch_bytes(void);
+
+/*
+ * b200q_qlinear_f16_i8 for callers that cannot provide scratch memory and cannot allocate any.
+ * No counterpart in the reference (its generated launch functions ask the runtime for a workspace).
+ *
+ * Meant for code that only holds device pointers and a stream: the launch function of a compiled
+ * graph, a plugin called from inside another runtime's loop, a process whose device memory is fully
+ * pre-partitioned.  Such code has no allocator to turn to and must not call cudaMalloc itself (it
+ * synchronises the device, can fail once memory is committed, and bypasses the host runtime's
+ * bookkeeping).  This entry point allocates nothing: the scratch is a fixed 512 KiB array inside the
+ * library's device image, held by every GPU that loads the library until the process exits.
+ *
+ *   - same operands and result as b200q_qlinear_f16_i8 with w_layout = B200Q_LAYOUT_KN; operands must
+ *     have 16-byte aligned bases and rows (N % 16 == 0, K % 8 == 0);
+ *   - a problem whose scratch requirement (b200q_qlinear_workspace_bytes) exceeds the built-in array
+ *     is refused with B200Q_WORKSPACE_TOO_SMALL and a message naming both sizes (most shapes need no
+ *     scratch; narrow, deep weights with 16 or more activation rows can exceed the array);
+ *   - the first call on a device looks up the array's device address (cudaGetSymbolAddress, with that
+ *     device current) and sets kernel attributes: make that first call before any stream capture;
+ *   - all calls on a device share the one array: calls that may overlap on the GPU (different
+ *     streams, or host threads launching concurrently) race on it.  Calls ordered on one stream are safe.
+ */
+B200Q_API int b200q_qlinear_f16_i8_static(const void *a, const void *wq, const void *scale, void *c, int64_t M, int64_t N,
+                                          int64_t K, int w_layout, void *stream);
+
+/*
  * Device-side status word of the calling thread's current device: 0 if no bounded wait of any
  * kernel launched so far has run out.  Synchronises the device.  A non-zero value is returned as
  * B200Q_KERNEL_TIMEOUT with the details in the error message, and the word is cleared.
