@@ -210,6 +210,77 @@ def make_quantized_stack(torch, hidet_b200, device, k: int, n: int, count: int, 
     return out
 
 
+def time_graph(torch, stream, fn, launches_per_call: int, min_calls: int = 5, min_ms: float = 20.0):
+    """Average device time of one launch of `fn`'s launches: `fn` is captured into a CUDA graph on
+    `stream` and replayed between two events until at least `min_ms` have passed."""
+    fn()
+    stream.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph, stream=stream):
+        fn()
+    for _ in range(3):
+        graph.replay()
+    calls = min_calls
+    while True:
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        stream.synchronize()
+        e0.record(stream)
+        for _ in range(calls):
+            graph.replay()
+        e1.record(stream)
+        stream.synchronize()
+        ms = e0.elapsed_time(e1)
+        if ms >= min_ms or calls >= 4096:
+            return ms * 1e3 / (calls * launches_per_call)
+        calls *= 4
+
+
+def extra_sections(torch, hidet_b200, device, stream, peaks):
+    """Prefill shapes and the quantize kernel, timed the same way; reported beside the headline."""
+    out = {}
+    prefill = []
+    for m, k, n in ((2048, 4096, 11008), (2048, 11008, 4096)):
+        stack = make_quantized_stack(torch, hidet_b200, device, k, n, 4, seed=k)
+        gen = torch.Generator(device=device).manual_seed(2)
+        a = torch.randn(m, k, generator=gen, device=device, dtype=torch.float32).to(torch.float16)
+        outs = [torch.empty(m, n, dtype=torch.float16, device=device) for _ in stack]
+
+        def fn():
+            for (wq, scale), c in zip(stack, outs):
+                hidet_b200.symmetric_quant_matmul(a, wq, scale, out=c)
+
+        us = time_graph(torch, stream, fn, len(stack))
+        flops = 2.0 * m * k * n
+        prefill.append({'M': m, 'K': k, 'N': n, 'us_per_launch': round(us, 2), 'TFLOPS': round(flops / us / 1e6, 1),
+                        'frac_of_bf16_burst_peak': round(flops / us / 1e6 / peaks['bf16_tflops'], 4),
+                        'frac_of_bf16_sustained_peak': round(flops / us / 1e6 / peaks['bf16_tflops_sustained'], 4)})
+        del stack, outs
+    out['prefill'] = prefill
+    k, n = 4096, 4096
+    gen = torch.Generator(device=device).manual_seed(3)
+    ws = [(torch.randn(k, n, generator=gen, device=device, dtype=torch.float32) * 0.02).to(torch.float16) for _ in range(8)]  # 268 MB > L2
+
+    def qfn():
+        for w in ws:
+            hidet_b200.symmetric_quantize(w, 'int8', dims=0)
+
+    # quantize allocates its outputs, which a graph capture cannot do: time eager launches with events
+    qfn()
+    stream.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record(stream)
+    reps = 10
+    for _ in range(reps):
+        qfn()
+    e1.record(stream)
+    stream.synchronize()
+    us = e0.elapsed_time(e1) * 1e3 / (reps * len(ws))
+    qbytes = 3 * k * n + 2 * n
+    out['quantize'] = {'K': k, 'N': n, 'dtype': 'f16->i8, dims=0', 'us_per_launch': round(us, 2), 'GBps': round(qbytes / us / 1e3, 1),
+                       'frac_of_hbm_peak': round(qbytes / us / 1e3 / peaks['hbm_gbs'], 4), 'timing': 'eager launches'}
+    return out
+
+
 def run_single_gpu(args) -> int:
     import torch
 
@@ -318,6 +389,12 @@ def run_single_gpu(args) -> int:
     e2e_ms = e0.elapsed_time(e1) / e2e_steps
     e2e_value = bytes_per_step / (e2e_ms * 1e-3) / 1e9
 
+    extras = {}
+    if not args.no_extras:
+        del stacks, outs
+        with torch.cuda.stream(side):
+            extras = extra_sections(torch, hidet_b200, device, side, peaks)
+
     status = hidet_b200.ffi.func('b200q_check_status')()
     assert status == 0
 
@@ -337,6 +414,7 @@ def run_single_gpu(args) -> int:
         'e2e': {'value': e2e_value, 'unit': 'GB/s', 'h2d_bytes_per_step': h2d, 'd2h_bytes_per_step': d2h, 'ms_per_step': e2e_ms,
                 'note': 'eager calls of hidet_b200.symmetric_quant_matmul, pinned host activations in and outputs out each step'},
     }
+    line.update(extras)
     if not args.no_cpu_baseline:
         line['cpu_baseline'] = cpu_baseline_block()
     print(json.dumps(line))
@@ -407,6 +485,7 @@ def main(argv=None) -> int:
     ap.add_argument('--warmup', type=int, default=3)
     ap.add_argument('--impl', choices=['ours', 'reference'], default='ours')
     ap.add_argument('--no-cpu-baseline', action='store_true', help='skip the CPU leg (for profiling runs)')
+    ap.add_argument('--no-extras', action='store_true', help='skip the prefill and quantize sections (for profiling runs)')
     ap.add_argument('--case', default=None, help='M,K,N: time one shape only (small case for profiling and tuning)')
     ap.add_argument('--layout', choices=['KN', 'NK'], default='KN', help='weight layout for --case')
     ap.add_argument('--launches', type=int, default=200, help='launches to time for --case')
