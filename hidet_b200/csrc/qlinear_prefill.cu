@@ -7,12 +7,12 @@
 // 4 KB + 8 KB of shared memory, the converters read 2 KB and write 4 KB, which leaves shared-memory
 // bandwidth headroom that the opposite assignment would not.
 //
-// One persistent CTA per SM, ten warps:
-//   warp 8      TMA producer: per 64-k stage one int8 tile [64 k][128 n] (plain layout) and one
+// One persistent CTA per SM, fourteen warps:
+//   warp 12     TMA producer: per 64-k stage one int8 tile [64 k][128 n] (plain layout) and one
 //               activation tile [256 m][64 k] f16 (128B swizzle = K-major MMA operand as is)
-//   warps 4-7   converters: int8 -> exact f16 in registers, written as the MN-major, 128B-swizzled MMA
+//   warps 4-11  converters: int8 -> exact f16 in registers, written as the MN-major, 128B-swizzled MMA
 //               operand ([2 column blocks][8 k-groups][8 k][64 n]), then a proxy fence and an mbarrier
-//   warp 9      MMA issuer (one lane): four K=16 MMAs per stage into one of two 256-column TMEM
+//   warp 13     MMA issuer (one lane): four K=16 MMAs per stage into one of two 256-column TMEM
 //               accumulators; tcgen05.commit frees the stage / publishes the accumulator
 //   warps 0-3   epilogue: tcgen05.ld of the accumulator (lane = weight column n, column = row m),
 //               times scale[n], one rounding to f16, stores to C[m, n]; overlaps the next tile's MMAs
@@ -39,8 +39,10 @@ constexpr int WF_BYTES = BK * TN * 2;       // converted f16 tile
 constexpr int ACT_BYTES = TM * BK * 2;      // activation tile
 constexpr int STAGE_BYTES = RAW_BYTES + WF_BYTES + ACT_BYTES;
 constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024;  // + alignment slack
-constexpr int THREADS = 320;
-constexpr int EPI_WARP0 = 0, CONV_WARP0 = 4, PRODUCER_WARP = 8, MMA_WARP = 9;
+constexpr int CONV_WARPS = 8;
+constexpr int EPI_WARP0 = 0, CONV_WARP0 = 4, PRODUCER_WARP = CONV_WARP0 + CONV_WARPS, MMA_WARP = PRODUCER_WARP + 1;
+constexpr int THREADS = 32 * (MMA_WARP + 1);
+constexpr int CONV_ROWS = CONV_WARPS * 4;    // k-rows the converters cover per pass (8 threads per row)
 constexpr uint32_t TMEM_COLS = 512;         // two accumulators of TM fp32 columns
 
 // tcgen05 instruction descriptor, kind::f16: D = f32, A = B = f16, A is MN-major, B is K-major,
@@ -128,7 +130,7 @@ __global__ void __launch_bounds__(THREADS, 1) qlinear_prefill_kn_kernel(const __
                                                                         const Params p) {
     extern __shared__ unsigned char smem_dyn[];
     __shared__ __align__(8) uint64_t tma_full[STAGES];   // TMA bytes of a stage have landed
-    __shared__ __align__(8) uint64_t conv_full[STAGES];  // the four converter warps have written the f16 tile
+    __shared__ __align__(8) uint64_t conv_full[STAGES];  // every converter warp has written its part of the f16 tile
     __shared__ __align__(8) uint64_t slot_free[STAGES];  // the MMAs that read the stage have completed
     __shared__ __align__(8) uint64_t acc_full[2];        // an accumulator holds a finished tile
     __shared__ __align__(8) uint64_t acc_empty[2];       // the four epilogue warps have read it out
@@ -148,7 +150,7 @@ __global__ void __launch_bounds__(THREADS, 1) qlinear_prefill_kn_kernel(const __
     if (threadIdx.x == 0) {
         for (int s = 0; s < STAGES; ++s) {
             mbar_init(smem_u32(&tma_full[s]), 1);
-            mbar_init(smem_u32(&conv_full[s]), 4);
+            mbar_init(smem_u32(&conv_full[s]), CONV_WARPS);
             mbar_init(smem_u32(&slot_free[s]), 1);
         }
         for (int b = 0; b < 2; ++b) {
@@ -227,11 +229,11 @@ __global__ void __launch_bounds__(THREADS, 1) qlinear_prefill_kn_kernel(const __
                 if (ok) umma_commit(smem_u32(&acc_full[buf]));
             }
         }
-    } else if (warp >= CONV_WARP0 && warp < CONV_WARP0 + 4) {
+    } else if (warp >= CONV_WARP0 && warp < CONV_WARP0 + CONV_WARPS) {
         // ---------------- converters ----------------
-        const int ct = threadIdx.x - CONV_WARP0 * 32;  // 0..127
+        const int ct = threadIdx.x - CONV_WARP0 * 32;  // 0 .. 32 * CONV_WARPS - 1
         const int ci = ct & 7;                         // 16-byte chunk of an int8 row: columns 16 ci .. 16 ci + 15
-        const int rb = ct >> 3;                        // row inside a pass of 16 rows
+        const int rb = ct >> 3;                        // row inside a pass of CONV_ROWS rows
         // f16 chunks (8 columns each) 2 ci and 2 ci + 1 of the 16 per row; chunk c lives in column block
         // c / 8 at slot (c % 8) ^ (k % 8) of its 128-byte row.  Half of the threads write the odd chunk
         // first so that the eight threads of a row hit eight different bank groups.
@@ -250,8 +252,8 @@ __global__ void __launch_bounds__(THREADS, 1) qlinear_prefill_kn_kernel(const __
                 }
                 const uint32_t raw = raw_addr(s), wf = wf_addr(s);
 #pragma unroll
-                for (int pass = 0; pass < BK / 16; ++pass) {
-                    const int k = pass * 16 + rb;
+                for (int pass = 0; pass < BK / CONV_ROWS; ++pass) {
+                    const int k = pass * CONV_ROWS + rb;
                     const uint4 v = lds128(raw + k * 128 + ci * 16);
                     uint32_t h[8];
                     cvt_s8x4_to_f16_pairs(v.x, h[0], h[1]);
