@@ -1,0 +1,144 @@
+"""The multi-GPU arm of bench.py: the 70B-shaped quantized linear, split column-parallel.
+
+One process per GPU (torch.distributed, NCCL).  W int8 [8192, 28672] is split along N over the ranks,
+activations fp16 [M, 8192] are replicated, every rank runs the single-GPU kernel on its shard and the
+fp16 output slices are all-gathered, so every rank ends with the full [M, 28672] output.  M is swept
+over {1, 16, 256, 2048}; a step is one pass over a rotation of distinct weight shards (larger than L2)
+for every M.  Strong scaling: the layer is the same at every GPU count, `value` counts the whole
+layer's algorithmic bytes, time is the maximum over ranks.
+"""
+from __future__ import annotations
+
+import json
+import os
+import time
+
+K_70B, N_70B = 8192, 28672
+MS_70B = (1, 16, 256, 2048)
+
+
+def algorithmic_bytes(m: int, k: int, n: int) -> int:
+    return k * n + 2 * m * k + 2 * n + 2 * m * n
+
+
+def run_sharded(args) -> int:
+    import torch
+    import torch.distributed as dist
+
+    import hidet_b200
+    from hidet_b200.distributed import ColumnParallelQuantLinear, column_range
+
+    rank = int(os.environ.get('RANK', '0'))
+    world = int(os.environ.get('WORLD_SIZE', str(args.gpus)))
+    local_rank = int(os.environ.get('LOCAL_RANK', str(rank)))
+    torch.cuda.set_device(local_rank)
+    device = torch.device('cuda', local_rank)
+    if not dist.is_initialized():
+        dist.init_process_group('nccl', device_id=device)
+
+    from bench import ClockSampler, measured_peaks  # the launcher script
+
+    peaks = measured_peaks()
+    k, n = K_70B, N_70B
+    begin, end = column_range(n, rank, world)
+    n_local = end - begin
+    copies = max(2, -(-(2 * 128 * 1024 * 1024) // (k * n_local)))
+    copies = min(copies, 16)
+
+    # Every rank draws the same full-width weights from the same seeds and keeps its columns.
+    layers = []
+    for i in range(copies):
+        gen = torch.Generator(device=device).manual_seed(100 + i)
+        w = (torch.randn(k, n, generator=gen, device=device, dtype=torch.float32) * 0.02).to(torch.float16)
+        layers.append(ColumnParallelQuantLinear.from_weight_shard(w[:, begin:end].contiguous()))
+        del w
+    gen = torch.Generator(device=device).manual_seed(1)
+    acts = {m: torch.randn(m, k, generator=gen, device=device, dtype=torch.float32).to(torch.float16) for m in MS_70B}
+
+    def step(ms=MS_70B):
+        out = None
+        for m in ms:
+            for layer in layers:
+                out = layer(acts[m])
+        return out
+
+    def timed(fn, reps):
+        dist.barrier()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(reps):
+            fn()
+        e1.record()
+        torch.cuda.synchronize()
+        dist.barrier()
+        t = torch.tensor([e0.elapsed_time(e1)], device=device, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item()) / reps
+
+    for _ in range(max(args.warmup, 3)):
+        step()
+    with ClockSampler(local_rank) as clocks:
+        time.sleep(0.15)
+        ms_per_step = timed(step, args.steps)
+        if ms_per_step * args.steps < 400.0:
+            for _ in range(int(400.0 / max(ms_per_step, 1e-3)) + 1):
+                step()
+            torch.cuda.synchronize()
+    bytes_per_step = sum(algorithmic_bytes(m, k, n) * copies for m in MS_70B)
+    flops_per_step = sum(2.0 * m * k * n * copies for m in MS_70B)
+    value = bytes_per_step / (ms_per_step * 1e-3) / 1e9
+
+    shapes = []
+    for m in MS_70B:
+        ms_m = timed(lambda: step((m,)), 5)
+        us = ms_m * 1e3 / copies
+        shapes.append({'M': m, 'K': k, 'N': n, 'us_per_layer': round(us, 2), 'GBps': round(algorithmic_bytes(m, k, n) / us / 1e3, 1),
+                       'TFLOPS': round(2.0 * m * k * n / us / 1e6, 2)})
+        # the same without the gather: what the collective costs
+        def local_only():
+            for layer in layers:
+                layer.local(acts[m])
+        us_local = timed(local_only, 5) * 1e3 / copies
+        shapes[-1]['us_local_kernel'] = round(us_local, 2)
+
+    # end to end: activations from pinned host memory in, gathered output back to the host, every step
+    pinned_in = {m: acts[m].cpu().pin_memory() for m in MS_70B}
+    pinned_out = {m: torch.empty(m, n, dtype=torch.float16).pin_memory() for m in MS_70B}
+
+    def e2e_step():
+        for m in MS_70B:
+            acts[m].copy_(pinned_in[m], non_blocking=True)
+            out = None
+            for layer in layers:
+                out = layer(acts[m])
+            pinned_out[m].copy_(out, non_blocking=True)
+        torch.cuda.current_stream().synchronize()
+
+    e2e_step()
+    e2e_ms = timed(e2e_step, max(args.steps // 2, 3))
+    e2e_value = bytes_per_step / (e2e_ms * 1e-3) / 1e9
+    assert hidet_b200.ffi.func('b200q_check_status')() == 0
+
+    if rank == 0:
+        line = {
+            'metric': 'quant-linear HBM GB/s (70B-shaped layer, column-parallel)', 'value': value, 'unit': 'GB/s', 'n_gpus': world,
+            'steps': args.steps, 'warmup': max(args.warmup, 3), 'ms_per_step': ms_per_step, 'higher_is_better': True,
+            'scaling': 'strong', 'vs_baseline': None, 'dtype': 'f16', 'accumulate': 'f32', 'weight_dtype': 'i8', 'data': 'synthetic',
+            'config': {'workload': 'sharded-70b-layer', 'K': k, 'N': n, 'M': list(MS_70B), 'parallelism': 'tp{} (columns) + all-gather'.format(world),
+                       'weights_in_rotation': copies, 'l2': 'inputs larger than L2: {} distinct weight shards of {} MB per rank'.format(copies, k * n_local // 1000000),
+                       'timing': 'eager launches, CUDA events, barrier on both sides, max over ranks'},
+            'tflops': flops_per_step / (ms_per_step * 1e-3) / 1e12,
+            'gpu_launches': len(MS_70B) * copies * args.steps,
+            'clocks': clocks.summary(),
+            'roofline': {'bound': 'hbm for M <= 16, tensor for M >= 256', 'achieved': value, 'peak': peaks['hbm_gbs'] * world, 'unit': 'GB/s',
+                         'frac': value / (peaks['hbm_gbs'] * world), 'traffic': None, 'peak_source': peaks['source'] + ' (burst copy) x n_gpus',
+                         'kernel': 'qlinear_decode_kn_kernel / qlinear_prefill_kn_kernel + ncclAllGather'},
+            'shapes': shapes,
+            'e2e': {'value': e2e_value, 'unit': 'GB/s', 'h2d_bytes_per_step': sum(t.numel() * 2 for t in pinned_in.values()),
+                    'd2h_bytes_per_step': sum(t.numel() * 2 for t in pinned_out.values()), 'ms_per_step': e2e_ms},
+        }
+        print(json.dumps(line))
+    dist.barrier()
+    dist.destroy_process_group()
+    return 0

@@ -1,0 +1,126 @@
+"""Column-parallel quantized linear over the GPUs of one node.
+
+The reference has no sharding layer: the user slices weights by hand and inserts collectives
+(examples/distributed/test.py); its collective op is an NCCL all-gather whose result is rank-major,
+``[nranks, *x.shape]`` (python/hidet/graph/ops/distributed.py:63-97).  This module provides that
+op with the same result layout, and on top of it the one strategy this path needs: split the weight
+along N, one process per GPU, gather the output slices.
+
+Per-output-channel quantization is column-local, so quantizing a column shard gives exactly the
+columns of the quantized full weight; a rank only ever needs its own shard.
+
+torch.distributed is the plumbing (NCCL on GPUs; the host logic also runs under gloo on CPU, where
+only the gathering can be exercised because the kernels are CUDA-only).
+"""
+from __future__ import annotations
+
+from typing import Optional, Tuple
+
+import torch
+import torch.distributed as dist
+
+
+def column_range(n: int, rank: int, world: int, multiple: int = 16) -> Tuple[int, int]:
+    """Columns [begin, end) of rank `rank`.  N must split into equal blocks that are multiples of
+    `multiple` columns (16 keeps every shard's rows 16-byte multiples for the TMA kernels)."""
+    if n % (world * multiple) != 0:
+        raise ValueError('N={} does not split into {} equal column blocks of a multiple of {}'.format(n, world, multiple))
+    step = n // world
+    return rank * step, (rank + 1) * step
+
+
+def shard_columns(weight: torch.Tensor, scale: Optional[torch.Tensor], rank: int, world: int):
+    """The contiguous column shard of a [K, N] weight (quantized or not) and of its [N] scale."""
+    begin, end = column_range(weight.shape[-1], rank, world)
+    w = weight[..., begin:end].contiguous()
+    s = scale[begin:end].contiguous() if scale is not None else None
+    return w, s
+
+
+def all_gather(x: torch.Tensor, group=None, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Rank-major gather, the reference op's contract: returns y[nranks, *x.shape] with y[r] = x of rank r."""
+    world = dist.get_world_size(group)
+    x = x.contiguous()
+    if out is None:
+        out = torch.empty((world,) + tuple(x.shape), dtype=x.dtype, device=x.device)
+    dist.all_gather_into_tensor(out.view(-1), x.view(-1), group=group)
+    return out
+
+
+def gather_columns(c_local: torch.Tensor, group=None, out: Optional[torch.Tensor] = None,
+                   staging: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Output slices c_local[..., M, N/g] of all ranks -> c[..., M, N] on every rank.
+
+    The all-gather delivers [g, M, N/g]; for a single row that already is [M, N]; otherwise one
+    strided copy puts the slices side by side."""
+    world = dist.get_world_size(group)
+    lead = tuple(c_local.shape[:-1])
+    n_local = c_local.shape[-1]
+    rows = 1
+    for d in lead:
+        rows *= d
+    gathered = all_gather(c_local.reshape(rows, n_local), group=group, out=staging)  # [g, rows, n_local]
+    if out is None:
+        out = torch.empty(lead + (world * n_local,), dtype=c_local.dtype, device=c_local.device)
+    if rows == 1:
+        out.view(-1).copy_(gathered.view(-1))
+    else:
+        out.view(rows, world, n_local).copy_(gathered.permute(1, 0, 2))
+    return out
+
+
+class ColumnParallelQuantLinear:
+    """y = x @ dequant(Wq, scale) with Wq[K, N] split along N over the ranks of `group`.
+
+    Build it from this rank's shard of the unquantized weight (`from_weight_shard`) or from an
+    already quantized shard.  `forward` runs the local quantized matmul and gathers the slices.
+    """
+
+    def __init__(self, wq_shard: torch.Tensor, scale_shard: torch.Tensor, group=None):
+        if wq_shard.dtype != torch.int8 or wq_shard.dim() != 2:
+            raise ValueError('expect an int8 [K, N/g] weight shard')
+        self.wq = wq_shard.contiguous()
+        self.scale = scale_shard.contiguous()
+        self.group = group
+        self.world = dist.get_world_size(group)
+        self.rank = dist.get_rank(group)
+        self._buffers = {}
+
+    @classmethod
+    def from_weight_shard(cls, w_shard: torch.Tensor, group=None):
+        from .quant import symmetric_quantize
+
+        wq, scale = symmetric_quantize(w_shard, 'int8', dims=0)
+        return cls(wq, scale, group)
+
+    @property
+    def in_features(self) -> int:
+        return self.wq.shape[0]
+
+    @property
+    def out_features(self) -> int:
+        return self.wq.shape[1] * self.world
+
+    def local(self, x: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+        from .quant import symmetric_quant_matmul
+
+        return symmetric_quant_matmul(x, self.wq, self.scale, out=out)
+
+    def forward(self, x: torch.Tensor) -> torch.Tensor:
+        lead = tuple(x.shape[:-1])
+        key = (lead, x.device)
+        if key not in self._buffers:  # static buffers: a decode loop calls this with the same shape every step
+            rows = 1
+            for d in lead:
+                rows *= d
+            n_local = self.wq.shape[1]
+            self._buffers[key] = (
+                torch.empty(lead + (n_local,), dtype=torch.float16, device=x.device),
+                torch.empty((self.world, rows, n_local), dtype=torch.float16, device=x.device),
+                torch.empty(lead + (self.out_features,), dtype=torch.float16, device=x.device),
+            )
+        c_local, staging, out = self._buffers[key]
+        self.local(x, out=c_local)
+        return gather_columns(c_local, self.group, out=out, staging=staging)
+
+    __call__ = forward
