@@ -50,7 +50,9 @@ def run_sharded(args) -> int:
     for i in range(copies):
         gen = torch.Generator(device=device).manual_seed(100 + i)
         w = (torch.randn(k, n, generator=gen, device=device, dtype=torch.float32) * 0.02).to(torch.float16)
-        layers.append(ColumnParallelQuantLinear.from_weight_shard(w[:, begin:end].contiguous()))
+        layers.append(ColumnParallelQuantLinear.from_weight_shard(w[:, begin:end].contiguous(), gather=args.gather))
+        if args.gather == 'p2p' and i > 0:
+            layers[-1].share_outputs_with(layers[0])
         del w
     gen = torch.Generator(device=device).manual_seed(1)
     acts = {m: torch.randn(m, k, generator=gen, device=device, dtype=torch.float32).to(torch.float16) for m in MS_70B}
@@ -125,7 +127,7 @@ def run_sharded(args) -> int:
             'metric': 'quant-linear HBM GB/s (70B-shaped layer, column-parallel)', 'value': value, 'unit': 'GB/s', 'n_gpus': world,
             'steps': args.steps, 'warmup': max(args.warmup, 3), 'ms_per_step': ms_per_step, 'higher_is_better': True,
             'scaling': 'strong', 'vs_baseline': None, 'dtype': 'f16', 'accumulate': 'f32', 'weight_dtype': 'i8', 'data': 'synthetic',
-            'config': {'workload': 'sharded-70b-layer', 'K': k, 'N': n, 'M': list(MS_70B), 'parallelism': 'tp{} (columns) + all-gather'.format(world),
+            'config': {'workload': 'sharded-70b-layer', 'K': k, 'N': n, 'M': list(MS_70B), 'parallelism': 'tp{} (columns), outputs by {}'.format(world, 'peer stores from the epilogue + barrier' if args.gather == 'p2p' else 'NCCL all-gather'),
                        'weights_in_rotation': copies, 'l2': 'inputs larger than L2: {} distinct weight shards of {} MB per rank'.format(copies, k * n_local // 1000000),
                        'timing': 'eager launches, CUDA events, barrier on both sides, max over ranks'},
             'tflops': flops_per_step / (ms_per_step * 1e-3) / 1e12,

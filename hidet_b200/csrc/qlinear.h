@@ -7,6 +7,18 @@
 
 namespace b200q {
 
+// Where a kernel writes its result.  Element (m, n) of the result goes to
+// ptr[i][m * ldc + col0 + n] for every i < count: one entry is the ordinary output; several entries
+// are the same column block of output buffers on several GPUs (peer-mapped pointers), which is how a
+// column-parallel layer delivers its slice to every rank without a separate all-gather.
+constexpr int kMaxOutTargets = 8;
+struct OutTargets {
+    void *ptr[kMaxOutTargets];
+    int count;
+    int64_t ldc;   // elements between consecutive rows of the destination
+    int64_t col0;  // first destination column
+};
+
 // How the small-M kernel splits a problem over CTAs, and the scratch that split needs.
 struct DecodePlan {
     int n_tiles = 0;
@@ -27,12 +39,12 @@ bool decode_kn_supported(const void *a, const void *wq, int64_t N, int64_t K);
 // c[M, N] = scale * (a[:, k_begin:k_end] x wq[k_begin:k_end, :]).  K is the row length of `a`.
 int launch_decode_kn(const void *a, const void *wq, const void *scale, void *c, int64_t M, int64_t N, int64_t K,
                      int64_t k_begin, int64_t k_end, bool allow_split, void *workspace, size_t workspace_bytes,
-                     cudaStream_t stream);
+                     cudaStream_t stream, const OutTargets *targets = nullptr);
 
 // The tensor-memory kernel for large M: same operand requirements as the small-M kernel.
 bool prefill_kn_supported(const void *a, const void *wq, int64_t N, int64_t K);
 int launch_prefill_kn(const void *a, const void *wq, const void *scale, void *c, int64_t M, int64_t N, int64_t K,
-                      cudaStream_t stream);
+                      cudaStream_t stream, const OutTargets *targets = nullptr);
 
 // Smallest M served by the tensor-memory kernel.  Its tile spans 256 activation rows, so below this
 // the small-M kernel, which re-streams the weight once per 16 rows, is still the faster one.

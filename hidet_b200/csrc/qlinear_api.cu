@@ -85,6 +85,33 @@ B200Q_API int b200q_qlinear_f16_i8(const void *a, const void *wq, const void *sc
     return launch_generic(a, wq, scale, c, M, N, K, 0, K, w_layout, s);
 }
 
+B200Q_API int b200q_qlinear_f16_i8_to_peers(const void *a, const void *wq, const void *scale, void *const *dst, int n_dst,
+                                            int64_t ldc, int64_t col_offset, int64_t M, int64_t N, int64_t K, void *workspace,
+                                            size_t workspace_bytes, void *stream) {
+    using namespace b200q;
+    if (n_dst < 1 || n_dst > kMaxOutTargets) return set_error(B200Q_INVALID_ARGUMENT, "qlinear_f16_i8_to_peers: n_dst must be 1..%d, got %d", kMaxOutTargets, n_dst);
+    if (dst == nullptr) return set_error(B200Q_INVALID_ARGUMENT, "qlinear_f16_i8_to_peers: null destination table");
+    if (col_offset < 0 || ldc < col_offset + N) return set_error(B200Q_INVALID_ARGUMENT, "qlinear_f16_i8_to_peers: columns [%lld, %lld) do not fit rows of %lld elements", (long long)col_offset, (long long)(col_offset + N), (long long)ldc);
+    int rc = check_qlinear_args("qlinear_f16_i8_to_peers", a, wq, scale, dst[0], M, N, K, B200Q_LAYOUT_KN);
+    if (rc != B200Q_OK) return rc;
+    if (M == 0 || N == 0) return B200Q_OK;
+    if (K == 0) return set_error(B200Q_INVALID_ARGUMENT, "qlinear_f16_i8_to_peers: K must be positive");
+    OutTargets t;
+    t.count = n_dst;
+    t.ldc = ldc;
+    t.col0 = col_offset;
+    for (int i = 0; i < n_dst; ++i) {
+        if (dst[i] == nullptr) return set_error(B200Q_INVALID_ARGUMENT, "qlinear_f16_i8_to_peers: destination %d is null", i);
+        t.ptr[i] = dst[i];
+    }
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    if (!decode_kn_supported(a, wq, N, K)) {
+        return set_error(B200Q_UNSUPPORTED, "qlinear_f16_i8_to_peers: operands need 16-byte aligned bases and rows (N %% 16 == 0, K %% 8 == 0)");
+    }
+    if (M >= kPrefillMinM) return launch_prefill_kn(a, wq, scale, dst[0], M, N, K, s, &t);
+    return launch_decode_kn(a, wq, scale, dst[0], M, N, K, 0, K, true, workspace, workspace_bytes, s, &t);
+}
+
 B200Q_API int b200q_qlinear_f16_i8_parts(const void *a, const void *wq, const void *scale, void *c, int64_t M,
                                          int64_t N, int64_t K, int k_parts, void *stream) {
     using namespace b200q;

@@ -121,9 +121,16 @@ __device__ __forceinline__ void st_cluster_f32(uint32_t addr, float v) {
 constexpr int kModeDirect = 0;  // one CTA per output tile
 constexpr int kModeSplit = 1;   // `splits` CTAs per tile: clusters of `cluster` CTAs, `groups` clusters per tile
 
+// One result element to every destination.
+__device__ __forceinline__ void store_out(const OutTargets &o, int row, int col, __half v) {
+    const size_t off = (size_t)row * o.ldc + o.col0 + col;
+#pragma unroll 1
+    for (int i = 0; i < o.count; ++i) static_cast<__half *>(o.ptr[i])[off] = v;
+}
+
 struct Params {
     const __half *scale;
-    __half *c;
+    OutTargets out;
     float *partial;           // [groups][M][N] fp32 in the workspace, used when groups > 1
     unsigned int *counters;   // [m_tiles * n_tiles * cluster] in the workspace, zero on entry, zero on exit
     unsigned int *status;
@@ -299,7 +306,7 @@ __global__ void __launch_bounds__(THREADS) qlinear_decode_kn_kernel(const __grid
 #pragma unroll
                             for (int e = 0; e < 2; ++e) {
                                 const int r = 8 * mt + 2 * t + e;
-                                if (r < rows) p.c[(size_t)(m0 + r) * p.N + nn] = __float2half_rn(acc[j][mt][2 * h + e] * sc);
+                                if (r < rows) store_out(p.out, m0 + r, nn, __float2half_rn(acc[j][mt][2 * h + e] * sc));
                             }
                     }
                 }
@@ -345,7 +352,7 @@ __global__ void __launch_bounds__(THREADS) qlinear_decode_kn_kernel(const __grid
             if (nn < p.N) {
                 float v = 0.0f;
                 for (uint32_t jr = 0; jr < nranks; ++jr) v += recv[((int)jr * BM + r) * cols_per + cc];
-                p.c[(size_t)(m0 + r) * p.N + nn] = __float2half_rn(v * __half2float(p.scale[nn]));
+                store_out(p.out, m0 + r, nn, __float2half_rn(v * __half2float(p.scale[nn])));
             }
         }
         TRACE(4);
@@ -384,7 +391,7 @@ __global__ void __launch_bounds__(THREADS) qlinear_decode_kn_kernel(const __grid
             float v = 0.0f;
 #pragma unroll 4
             for (int gr = 0; gr < p.groups; ++gr) v += __ldcg(&p.partial[((size_t)gr * p.M + (m0 + r)) * p.N + nn]);
-            p.c[(size_t)(m0 + r) * p.N + nn] = __float2half_rn(v * __half2float(p.scale[nn]));
+            store_out(p.out, m0 + r, nn, __float2half_rn(v * __half2float(p.scale[nn])));
         }
     }
     if (threadIdx.x == 0) p.counters[slot] = 0;  // leave the workspace ready for the next call
@@ -433,7 +440,7 @@ bool decode_kn_supported(const void *a, const void *wq, int64_t N, int64_t K) {
 
 int launch_decode_kn(const void *a, const void *wq, const void *scale, void *c, int64_t M, int64_t N, int64_t K,
                      int64_t k_begin, int64_t k_end, bool allow_split, void *workspace, size_t workspace_bytes,
-                     cudaStream_t stream) {
+                     cudaStream_t stream, const OutTargets *targets) {
     using namespace decode;
     DecodePlan pl = plan_decode(M, N, k_end - k_begin);
     if (!allow_split) {
@@ -460,7 +467,14 @@ int launch_decode_kn(const void *a, const void *wq, const void *scale, void *c, 
 
     Params p;
     p.scale = static_cast<const __half *>(scale);
-    p.c = static_cast<__half *>(c);
+    if (targets != nullptr) {
+        p.out = *targets;
+    } else {
+        p.out.ptr[0] = c;
+        p.out.count = 1;
+        p.out.ldc = N;
+        p.out.col0 = 0;
+    }
     p.counters = static_cast<unsigned int *>(workspace);
     p.partial = pl.partial_bytes > 0 ? reinterpret_cast<float *>(static_cast<unsigned char *>(workspace) + pl.counter_bytes) : nullptr;
     p.status = device_status_word();

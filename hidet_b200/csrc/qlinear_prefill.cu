@@ -119,7 +119,7 @@ __device__ __forceinline__ void cvt_s8x4_to_f16_pairs(uint32_t v, uint32_t &p01,
 
 struct Params {
     const __half *scale;
-    __half *c;
+    OutTargets out;
     unsigned int *status;
     int M, N, K;
     int n_tiles, m_tiles;
@@ -292,7 +292,7 @@ __global__ void __launch_bounds__(THREADS, 1) qlinear_prefill_kn_kernel(const __
             const int n = n0 + 32 * q + lane;
             const bool n_ok = n < p.N;
             const float sc = n_ok ? __half2float(p.scale[n]) : 0.0f;
-            __half *dst = p.c + (size_t)m0 * p.N + n;
+            const size_t dst_off = (size_t)m0 * p.out.ldc + p.out.col0 + n;
             const int m_left = p.M - m0;
 #pragma unroll 1
             for (int cb = 0; cb < TM / 32; ++cb) {
@@ -300,10 +300,16 @@ __global__ void __launch_bounds__(THREADS, 1) qlinear_prefill_kn_kernel(const __
                 tmem_ld_32x32(tmem_base + ((uint32_t)(32 * q) << 16) + buf * TM + cb * 32, v);
                 tmem_ld_wait();
                 if (n_ok) {
+                    __half h[32];
 #pragma unroll
-                    for (int j = 0; j < 32; ++j) {
-                        const int m = cb * 32 + j;
-                        if (m < m_left) dst[(size_t)m * p.N] = __float2half_rn(__uint_as_float(v[j]) * sc);
+                    for (int j = 0; j < 32; ++j) h[j] = __float2half_rn(__uint_as_float(v[j]) * sc);
+#pragma unroll 1
+                    for (int t = 0; t < p.out.count; ++t) {
+                        __half *dst = static_cast<__half *>(p.out.ptr[t]) + dst_off + (size_t)(cb * 32) * p.out.ldc;
+#pragma unroll
+                        for (int j = 0; j < 32; ++j) {
+                            if (cb * 32 + j < m_left) dst[(size_t)j * p.out.ldc] = h[j];
+                        }
                     }
                 }
             }
@@ -330,7 +336,7 @@ bool prefill_kn_supported(const void *a, const void *wq, int64_t N, int64_t K) {
 }
 
 int launch_prefill_kn(const void *a, const void *wq, const void *scale, void *c, int64_t M, int64_t N, int64_t K,
-                      cudaStream_t stream) {
+                      cudaStream_t stream, const OutTargets *targets) {
     using namespace prefill;
     CUtensorMap map_w, map_a;
     int rc = make_tensor_map_2d(&map_w, CU_TENSOR_MAP_DATA_TYPE_UINT8, wq, (uint64_t)N, (uint64_t)K, (uint64_t)N, TN, BK,
@@ -342,7 +348,14 @@ int launch_prefill_kn(const void *a, const void *wq, const void *scale, void *c,
 
     Params p;
     p.scale = static_cast<const __half *>(scale);
-    p.c = static_cast<__half *>(c);
+    if (targets != nullptr) {
+        p.out = *targets;
+    } else {
+        p.out.ptr[0] = c;
+        p.out.count = 1;
+        p.out.ldc = N;
+        p.out.col0 = 0;
+    }
     p.status = device_status_word();
     p.M = (int)M;
     p.N = (int)N;

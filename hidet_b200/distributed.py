@@ -69,29 +69,73 @@ def gather_columns(c_local: torch.Tensor, group=None, out: Optional[torch.Tensor
     return out
 
 
+class PeerOutput:
+    """A [rows, cols] float16 output buffer that exists on every rank of the group and that every
+    rank can store into directly: symmetric memory (torch.distributed._symmetric_memory), i.e. the
+    same allocation on every GPU, peer-mapped over NVLink.  Two copies are kept and used in turn, so
+    that a rank may still read the previous result while its peers already write the next one.
+    """
+
+    def __init__(self, rows: int, cols: int, device: torch.device, group=None):
+        import torch.distributed._symmetric_memory as symm_mem
+
+        group = group if group is not None else dist.group.WORLD
+        self.buffers, self.handles, self.ptr_tables = [], [], []
+        for _ in range(2):
+            buf = symm_mem.empty((rows, cols), dtype=torch.float16, device=device)
+            handle = symm_mem.rendezvous(buf, group)
+            self.buffers.append(buf)
+            self.handles.append(handle)
+            self.ptr_tables.append([int(p) for p in handle.buffer_ptrs])
+        self.turn = 0
+
+    def next(self):
+        """(local buffer, table of every rank's pointer to its copy, handle) for the next result."""
+        i = self.turn
+        self.turn ^= 1
+        return self.buffers[i], self.ptr_tables[i], self.handles[i]
+
+
 class ColumnParallelQuantLinear:
     """y = x @ dequant(Wq, scale) with Wq[K, N] split along N over the ranks of `group`.
 
     Build it from this rank's shard of the unquantized weight (`from_weight_shard`) or from an
-    already quantized shard.  `forward` runs the local quantized matmul and gathers the slices.
+    already quantized shard.  `forward` runs the local quantized matmul and delivers the slices:
+
+    gather='nccl'  the local kernel writes its slice, an NCCL all-gather collects the slices
+                   (rank-major, as the reference's all-gather op) and one copy puts them side by side;
+    gather='p2p'   the local kernel's epilogue stores its columns straight into every rank's [M, N]
+                   output over NVLink (b200q_qlinear_f16_i8_to_peers), then one cross-rank barrier on
+                   the stream: no staging buffer, no reshuffle, no collective launch.
     """
 
-    def __init__(self, wq_shard: torch.Tensor, scale_shard: torch.Tensor, group=None):
+    def __init__(self, wq_shard: torch.Tensor, scale_shard: torch.Tensor, group=None, gather: str = 'nccl'):
         if wq_shard.dtype != torch.int8 or wq_shard.dim() != 2:
             raise ValueError('expect an int8 [K, N/g] weight shard')
+        if gather not in ('nccl', 'p2p'):
+            raise ValueError("gather must be 'nccl' or 'p2p', got {!r}".format(gather))
         self.wq = wq_shard.contiguous()
         self.scale = scale_shard.contiguous()
         self.group = group
+        self.gather = gather
         self.world = dist.get_world_size(group)
         self.rank = dist.get_rank(group)
+        if gather == 'p2p' and self.world > 8:
+            raise ValueError('peer stores serve up to 8 ranks, got {}'.format(self.world))
         self._buffers = {}
+        self._peer_outputs = {}
 
     @classmethod
-    def from_weight_shard(cls, w_shard: torch.Tensor, group=None):
+    def from_weight_shard(cls, w_shard: torch.Tensor, group=None, gather: str = 'nccl'):
         from .quant import symmetric_quantize
 
         wq, scale = symmetric_quantize(w_shard, 'int8', dims=0)
-        return cls(wq, scale, group)
+        return cls(wq, scale, group, gather)
+
+    def share_outputs_with(self, other: 'ColumnParallelQuantLinear') -> None:
+        """Use `other`'s peer-mapped output buffers (layers of equal width that run one after the
+        other can share them; every layer that owns its own costs two [M, N] buffers per shape)."""
+        self._peer_outputs = other._peer_outputs
 
     @property
     def in_features(self) -> int:
@@ -106,7 +150,37 @@ class ColumnParallelQuantLinear:
 
         return symmetric_quant_matmul(x, self.wq, self.scale, out=out)
 
+    def _forward_p2p(self, x: torch.Tensor) -> torch.Tensor:
+        import ctypes
+
+        from . import ffi
+        from .runtime import current_stream_ptr, workspaces
+
+        lead = tuple(x.shape[:-1])
+        rows = 1
+        for d in lead:
+            rows *= d
+        k, n_local = self.wq.shape
+        n = n_local * self.world
+        key = (rows, x.device)
+        if key not in self._peer_outputs:
+            self._peer_outputs[key] = PeerOutput(rows, n, x.device, self.group)
+        out, ptrs, handle = self._peer_outputs[key].next()
+        table = (ctypes.c_void_p * self.world)(*ptrs)
+        x = x.contiguous()
+        with torch.cuda.device(x.device):
+            ws_bytes = ffi.func('b200q_qlinear_workspace_bytes')(rows, n_local, k, ffi.LAYOUT_KN)
+            ws_ptr, ws_size = workspaces.get(x.device, ws_bytes)
+            ffi.func('b200q_qlinear_f16_i8_to_peers')(
+                x.data_ptr(), self.wq.data_ptr(), self.scale.data_ptr(), table, self.world, n, self.rank * n_local, rows, n_local, k,
+                ws_ptr, ws_size, current_stream_ptr(x.device),
+            )
+            handle.barrier(channel=0)  # on the current stream: every rank's stores have landed everywhere
+        return out.view(lead + (n,))
+
     def forward(self, x: torch.Tensor) -> torch.Tensor:
+        if self.gather == 'p2p':
+            return self._forward_p2p(x)
         lead = tuple(x.shape[:-1])
         key = (lead, x.device)
         if key not in self._buffers:  # static buffers: a decode loop calls this with the same shape every step

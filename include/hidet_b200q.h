@@ -124,6 +124,21 @@ B200Q_API int b200q_qlinear_f16_i8_parts(const void *a, const void *wq, const vo
                                          int64_t N, int64_t K, int k_parts, void *stream);
 
 /*
+ * The quantized linear of one rank of a column-parallel layer, delivering its result to every rank:
+ * element (m, n) of a[M, K] x dequant(wq[K, N], scale[N]) is stored to
+ * dst[i][m * ldc + col_offset + n] for each of the n_dst destinations (1 <= n_dst <= 8).  The
+ * destinations are the [M, ldc] output buffers of the ranks, this rank's own included, given as
+ * pointers valid on this device (peer-mapped for the other GPUs); the stores are plain peer stores
+ * from the kernel's epilogue.  Replaces the matmul followed by the all-gather op of
+ * python/hidet/graph/ops/distributed.py:63-97 (whose result is rank-major and needs a reshuffle).
+ * The caller orders the ranks afterwards (a barrier between "all kernels done" and "outputs read").
+ * `dst` is a host array.  KN layout; workspace as for b200q_qlinear_f16_i8 with the same M, N, K.
+ */
+B200Q_API int b200q_qlinear_f16_i8_to_peers(const void *a, const void *wq, const void *scale, void *const *dst, int n_dst,
+                                            int64_t ldc, int64_t col_offset, int64_t M, int64_t N, int64_t K, void *workspace,
+                                            size_t workspace_bytes, void *stream);
+
+/*
  * Bytes of the scratch array built into the library for b200q_qlinear_f16_i8_static (512 KiB).
  * No counterpart in the reference.
  */
