@@ -490,7 +490,7 @@ def main(argv=None) -> int:
     ap.add_argument('--case', default=None, help='M,K,N: time one shape only (small case for profiling and tuning)')
     ap.add_argument('--layout', choices=['KN', 'NK'], default='KN', help='weight layout for --case')
     ap.add_argument('--launches', type=int, default=200, help='launches to time for --case')
-    ap.add_argument('--eager', action='store_true', help='--case: launch one by one instead of replaying a CUDA graph')
+    ap.add_argument('--eager', action='store_true', help='launch one by one instead of replaying a CUDA graph (--case and multi-GPU)')
     args = ap.parse_args(argv)
     if args.case:
         return run_case(args)
