@@ -46,8 +46,15 @@ bool prefill_kn_supported(const void *a, const void *wq, int64_t N, int64_t K);
 int launch_prefill_kn(const void *a, const void *wq, const void *scale, void *c, int64_t M, int64_t N, int64_t K,
                       cudaStream_t stream, const OutTargets *targets = nullptr);
 
-// Smallest M served by the tensor-memory kernel.  Its tile spans 256 activation rows, so below this
-// the small-M kernel, which re-streams the weight once per 16 rows, is still the faster one.
+// Which kernel serves M activation rows.  The tensor-memory kernel's tiles span 64 or 256 rows and it
+// streams every weight tile once per row block; the small-M kernel re-streams the weight once per 16
+// rows (from L2 after the first pass).  Up to 32 rows the small-M kernel always wins, up to 64 rows it
+// still wins on weights of a few tens of MB.
 constexpr int64_t kPrefillMinM = 33;
+inline bool use_prefill_kernel(int64_t M, int64_t N, int64_t K) {
+    if (M < kPrefillMinM) return false;
+    if (M <= 64) return K * N > (int64_t)24 * 1024 * 1024;
+    return true;
+}
 
 }  // namespace b200q

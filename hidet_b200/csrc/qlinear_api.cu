@@ -76,7 +76,7 @@ B200Q_API int b200q_qlinear_f16_i8(const void *a, const void *wq, const void *sc
         B200Q_CUDA_TRY(cudaMemsetAsync(c, 0, (size_t)M * N * sizeof(__half), s));
         return B200Q_OK;
     }
-    if (w_layout == B200Q_LAYOUT_KN && M >= kPrefillMinM && prefill_kn_supported(a, wq, N, K)) {
+    if (w_layout == B200Q_LAYOUT_KN && use_prefill_kernel(M, N, K) && prefill_kn_supported(a, wq, N, K)) {
         return launch_prefill_kn(a, wq, scale, c, M, N, K, s);
     }
     if (w_layout == B200Q_LAYOUT_KN && decode_kn_supported(a, wq, N, K)) {
@@ -108,7 +108,7 @@ B200Q_API int b200q_qlinear_f16_i8_to_peers(const void *a, const void *wq, const
     if (!decode_kn_supported(a, wq, N, K)) {
         return set_error(B200Q_UNSUPPORTED, "qlinear_f16_i8_to_peers: operands need 16-byte aligned bases and rows (N %% 16 == 0, K %% 8 == 0)");
     }
-    if (M >= kPrefillMinM) return launch_prefill_kn(a, wq, scale, dst[0], M, N, K, s, &t);
+    if (use_prefill_kernel(M, N, K)) return launch_prefill_kn(a, wq, scale, dst[0], M, N, K, s, &t);
     return launch_decode_kn(a, wq, scale, dst[0], M, N, K, 0, K, true, workspace, workspace_bytes, s, &t);
 }
 

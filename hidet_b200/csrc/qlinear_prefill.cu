@@ -8,14 +8,17 @@
 // bandwidth headroom that the opposite assignment would not.
 //
 // One persistent CTA per SM, fourteen warps:
-//   warp 12     TMA producer: per 64-k stage one int8 tile [64 k][128 n] (plain layout) and one
-//               activation tile [256 m][64 k] f16 (128B swizzle = K-major MMA operand as is)
+//   warp 12     TMA producer: per 64-k stage one int8 tile [64 k][128 n] (plain layout, its own short
+//               ring) and one activation tile [TM m][64 k] f16 (128B swizzle = K-major MMA operand as is);
+//               TM = 256, or 64 when that fills more SMs
 //   warps 4-11  converters: int8 -> exact f16 in registers, written as the MN-major, 128B-swizzled MMA
 //               operand ([2 column blocks][8 k-groups][8 k][64 n]), then a proxy fence and an mbarrier
 //   warp 13     MMA issuer (one lane): four K=16 MMAs per stage into one of two 256-column TMEM
 //               accumulators; tcgen05.commit frees the stage / publishes the accumulator
 //   warps 0-3   epilogue: tcgen05.ld of the accumulator (lane = weight column n, column = row m),
-//               times scale[n], one rounding to f16, stores to C[m, n]; overlaps the next tile's MMAs
+//               times scale[n], one rounding to f16, transposed through a small staging buffer and
+//               written as 256-byte rows with 16-byte stores to C[m, n] (of every destination, for the
+//               column-parallel layer); overlaps the next tile's MMAs
 // Rows beyond M, columns beyond N and k beyond K are zero-filled by TMA and never stored.
 //
 // Every wait is bounded: a wait that runs out records where in the device status word, the role
@@ -31,23 +34,33 @@ namespace b200q {
 namespace prefill {
 
 constexpr int TN = 128;                     // weight columns per tile = MMA M
-constexpr int TM = 256;                     // activation rows per tile = MMA N
 constexpr int BK = 64;                      // k per stage = four MMAs of K = 16
-constexpr int STAGES = 4;
 constexpr int RAW_BYTES = BK * TN;          // int8 tile
 constexpr int WF_BYTES = BK * TN * 2;       // converted f16 tile
-constexpr int ACT_BYTES = TM * BK * 2;      // activation tile
-constexpr int STAGE_BYTES = RAW_BYTES + WF_BYTES + ACT_BYTES;
-constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024;  // + alignment slack
 constexpr int CONV_WARPS = 8;
 constexpr int EPI_WARP0 = 0, CONV_WARP0 = 4, PRODUCER_WARP = CONV_WARP0 + CONV_WARPS, MMA_WARP = PRODUCER_WARP + 1;
 constexpr int THREADS = 32 * (MMA_WARP + 1);
-constexpr int CONV_ROWS = CONV_WARPS * 4;    // k-rows the converters cover per pass (8 threads per row)
-constexpr uint32_t TMEM_COLS = 512;         // two accumulators of TM fp32 columns
+constexpr int STAGE_ROW_BYTES = TN * 2 + 16; // one output row of a tile in the epilogue's staging buffer, padded
+constexpr int STAGING_BYTES = 32 * STAGE_ROW_BYTES;
 
-// tcgen05 instruction descriptor, kind::f16: D = f32, A = B = f16, A is MN-major, B is K-major,
-// N = 256 (bits 17..22 hold N / 8), M = 128 (bits 24..28 hold M / 16).
-constexpr uint32_t kInstrDesc = (1u << 4) | (1u << 15) | ((uint32_t)(TM >> 3) << 17) | ((uint32_t)(TN >> 4) << 24);
+// Per activation-tile height TM (= MMA N): ring depths and the shared-memory budget.
+template <int TM>
+struct Config {
+    static constexpr int ACT_BYTES = TM * BK * 2;
+    static constexpr int STAGES = TM == 256 ? 4 : 6;         // f16 weight + activation ring, consumed by the MMAs
+    static constexpr int RAW_SLOTS = TM == 256 ? 3 : 4;      // int8 ring, consumed by the converters
+    // Converter warps form groups that take stages in turn, so that the load-convert-store-fence latency
+    // of one stage overlaps that of the next ones (the ring must hold the stages being converted plus two).
+    static constexpr int CONV_GROUPS = TM == 256 ? 2 : 4;
+    static constexpr int GROUP_WARPS = CONV_WARPS / CONV_GROUPS;
+    static constexpr int CONV_ROWS = GROUP_WARPS * 4;        // k-rows a group covers per pass (8 threads per row)
+    static constexpr int MAIN_BYTES = ACT_BYTES + WF_BYTES;
+    static constexpr int SMEM_BYTES = STAGES * MAIN_BYTES + RAW_SLOTS * RAW_BYTES + STAGING_BYTES + 1024;  // + alignment slack
+    static constexpr uint32_t TMEM_COLS = 2 * TM;            // two accumulators of TM fp32 columns (a power of two >= 32)
+    // tcgen05 instruction descriptor, kind::f16: D = f32, A = B = f16, A is MN-major, B is K-major,
+    // N = TM (bits 17..22 hold N / 8), M = 128 (bits 24..28 hold M / 16).
+    static constexpr uint32_t kInstrDesc = (1u << 4) | (1u << 15) | ((uint32_t)(TM >> 3) << 17) | ((uint32_t)(TN >> 4) << 24);
+};
 
 // Shared-memory matrix descriptor: start address, leading / stride byte offsets (all in 16-byte
 // units), descriptor version 1, 128-byte swizzle.
@@ -125,32 +138,44 @@ struct Params {
     int n_tiles, m_tiles;
 };
 
+template <int TM>
 __global__ void __launch_bounds__(THREADS, 1) qlinear_prefill_kn_kernel(const __grid_constant__ CUtensorMap map_w,
                                                                         const __grid_constant__ CUtensorMap map_a,
                                                                         const Params p) {
+    using Cfg = Config<TM>;
+    constexpr int STAGES = Cfg::STAGES, RAW_SLOTS = Cfg::RAW_SLOTS;
+    constexpr int CONV_GROUPS = Cfg::CONV_GROUPS, GROUP_WARPS = Cfg::GROUP_WARPS, CONV_ROWS = Cfg::CONV_ROWS;
     extern __shared__ unsigned char smem_dyn[];
-    __shared__ __align__(8) uint64_t tma_full[STAGES];   // TMA bytes of a stage have landed
-    __shared__ __align__(8) uint64_t conv_full[STAGES];  // every converter warp has written its part of the f16 tile
-    __shared__ __align__(8) uint64_t slot_free[STAGES];  // the MMAs that read the stage have completed
-    __shared__ __align__(8) uint64_t acc_full[2];        // an accumulator holds a finished tile
-    __shared__ __align__(8) uint64_t acc_empty[2];       // the four epilogue warps have read it out
+    __shared__ __align__(8) uint64_t raw_full[RAW_SLOTS];   // an int8 tile has landed
+    __shared__ __align__(8) uint64_t raw_empty[RAW_SLOTS];  // the converter group of that stage has read it
+    __shared__ __align__(8) uint64_t act_full[STAGES];      // an activation tile has landed
+    __shared__ __align__(8) uint64_t conv_full[STAGES];     // the converter group of that stage has written the f16 tile
+    __shared__ __align__(8) uint64_t slot_free[STAGES];     // the MMAs that read the stage have completed
+    __shared__ __align__(8) uint64_t acc_full[2];           // an accumulator holds a finished tile
+    __shared__ __align__(8) uint64_t acc_empty[2];          // the four epilogue warps have read it out
     __shared__ uint32_t tmem_base_slot;
 
     const uint32_t smem_base = (smem_u32(smem_dyn) + 1023u) & ~1023u;  // swizzled operands need 1024-byte alignment
+    unsigned char *smem_gen = smem_dyn + (smem_base - smem_u32(smem_dyn));
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
     const int total_tiles = p.n_tiles * p.m_tiles;
     const int k_blocks = (p.K + BK - 1) / BK;
 
-    // stage layout: [activations 32 KB][f16 weights 16 KB][int8 weights 8 KB]
-    auto act_addr = [&](int s) { return smem_base + s * STAGE_BYTES; };
-    auto wf_addr = [&](int s) { return smem_base + s * STAGE_BYTES + ACT_BYTES; };
-    auto raw_addr = [&](int s) { return smem_base + s * STAGE_BYTES + ACT_BYTES + WF_BYTES; };
+    // layout: STAGES x [activations][f16 weights], RAW_SLOTS x [int8 weights], epilogue staging
+    auto act_addr = [&](int s) { return smem_base + s * Cfg::MAIN_BYTES; };
+    auto wf_addr = [&](int s) { return smem_base + s * Cfg::MAIN_BYTES + Cfg::ACT_BYTES; };
+    auto raw_addr = [&](int r) { return smem_base + STAGES * Cfg::MAIN_BYTES + r * RAW_BYTES; };
+    constexpr int STAGING_OFF = STAGES * Cfg::MAIN_BYTES + RAW_SLOTS * RAW_BYTES;
 
     if (threadIdx.x == 0) {
+        for (int r = 0; r < RAW_SLOTS; ++r) {
+            mbar_init(smem_u32(&raw_full[r]), 1);
+            mbar_init(smem_u32(&raw_empty[r]), GROUP_WARPS);
+        }
         for (int s = 0; s < STAGES; ++s) {
-            mbar_init(smem_u32(&tma_full[s]), 1);
-            mbar_init(smem_u32(&conv_full[s]), CONV_WARPS);
+            mbar_init(smem_u32(&act_full[s]), 1);
+            mbar_init(smem_u32(&conv_full[s]), GROUP_WARPS);
             mbar_init(smem_u32(&slot_free[s]), 1);
         }
         for (int b = 0; b < 2; ++b) {
@@ -160,7 +185,7 @@ __global__ void __launch_bounds__(THREADS, 1) qlinear_prefill_kn_kernel(const __
         mbar_fence_init();
     }
     if (warp == MMA_WARP) {
-        tmem_alloc(smem_u32(&tmem_base_slot), TMEM_COLS);
+        tmem_alloc(smem_u32(&tmem_base_slot), Cfg::TMEM_COLS);
         tmem_relinquish();
     }
     tc_fence_before_sync();
@@ -180,17 +205,24 @@ __global__ void __launch_bounds__(THREADS, 1) qlinear_prefill_kn_kernel(const __
                 const int n0 = (tile % p.n_tiles) * TN;
                 const int m0 = (tile / p.n_tiles) * TM;
                 for (int kb = 0; kb < k_blocks; ++kb, ++i) {
-                    const int s = i % STAGES;
-                    const uint32_t use = i / STAGES;
-                    if (use >= 1 && !mbar_wait(smem_u32(&slot_free[s]), (use - 1) & 1)) {
+                    const int r = i % RAW_SLOTS;
+                    const uint32_t use_r = i / RAW_SLOTS;
+                    if (use_r >= 1 && !mbar_wait(smem_u32(&raw_empty[r]), (use_r - 1) & 1)) {
                         report_timeout(p.status, kKernelPrefill, 1);
                         ok = false;
                         break;
                     }
-                    const uint32_t bar = smem_u32(&tma_full[s]);
-                    mbar_expect_tx(bar, RAW_BYTES + ACT_BYTES);
-                    tma_load_2d_hint(raw_addr(s), &map_w, n0, kb * BK, bar, keep);
-                    tma_load_2d_hint(act_addr(s), &map_a, kb * BK, m0, bar, keep);
+                    mbar_expect_tx(smem_u32(&raw_full[r]), RAW_BYTES);
+                    tma_load_2d_hint(raw_addr(r), &map_w, n0, kb * BK, smem_u32(&raw_full[r]), keep);
+                    const int s = i % STAGES;
+                    const uint32_t use = i / STAGES;
+                    if (use >= 1 && !mbar_wait(smem_u32(&slot_free[s]), (use - 1) & 1)) {
+                        report_timeout(p.status, kKernelPrefill, 6);
+                        ok = false;
+                        break;
+                    }
+                    mbar_expect_tx(smem_u32(&act_full[s]), Cfg::ACT_BYTES);
+                    tma_load_2d_hint(act_addr(s), &map_a, kb * BK, m0, smem_u32(&act_full[s]), keep);
                 }
             }
         }
@@ -210,7 +242,7 @@ __global__ void __launch_bounds__(THREADS, 1) qlinear_prefill_kn_kernel(const __
                 for (int kb = 0; kb < k_blocks; ++kb, ++i) {
                     const int s = i % STAGES;
                     const uint32_t use = i / STAGES;
-                    if (!mbar_wait(smem_u32(&tma_full[s]), use & 1) || !mbar_wait(smem_u32(&conv_full[s]), use & 1)) {
+                    if (!mbar_wait(smem_u32(&act_full[s]), use & 1) || !mbar_wait(smem_u32(&conv_full[s]), use & 1)) {
                         report_timeout(p.status, kKernelPrefill, 3);
                         ok = false;
                         break;
@@ -222,7 +254,7 @@ __global__ void __launch_bounds__(THREADS, 1) qlinear_prefill_kn_kernel(const __
                         const uint64_t da = smem_desc(wf_addr(s) + ks * 2048, 8192, 1024);
                         // B: K-major activations, 8-row groups 1024 B apart; K = 16 is 32 bytes along the swizzled row.
                         const uint64_t db = smem_desc(act_addr(s) + ks * 32, 16, 1024);
-                        umma_f16(d_addr, da, db, kInstrDesc, (kb > 0 || ks > 0) ? 1u : 0u);
+                        umma_f16(d_addr, da, db, Cfg::kInstrDesc, (kb > 0 || ks > 0) ? 1u : 0u);
                     }
                     umma_commit(smem_u32(&slot_free[s]));
                 }
@@ -231,7 +263,9 @@ __global__ void __launch_bounds__(THREADS, 1) qlinear_prefill_kn_kernel(const __
         }
     } else if (warp >= CONV_WARP0 && warp < CONV_WARP0 + CONV_WARPS) {
         // ---------------- converters ----------------
-        const int ct = threadIdx.x - CONV_WARP0 * 32;  // 0 .. 32 * CONV_WARPS - 1
+        const int cw = warp - CONV_WARP0;
+        const int group = cw % CONV_GROUPS;            // this warp's group converts stages group, group + CONV_GROUPS, ...
+        const int ct = (cw / CONV_GROUPS) * 32 + lane; // 0 .. 32 * GROUP_WARPS - 1 inside the group
         const int ci = ct & 7;                         // 16-byte chunk of an int8 row: columns 16 ci .. 16 ci + 15
         const int rb = ct >> 3;                        // row inside a pass of CONV_ROWS rows
         // f16 chunks (8 columns each) 2 ci and 2 ci + 1 of the 16 per row; chunk c lives in column block
@@ -243,23 +277,32 @@ __global__ void __launch_bounds__(THREADS, 1) qlinear_prefill_kn_kernel(const __
         bool ok = true;
         for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
             for (int kb = 0; kb < k_blocks; ++kb, ++i) {
+                if ((int)(i % CONV_GROUPS) != group) continue;
+                const int r = i % RAW_SLOTS;
+                const uint32_t use_r = i / RAW_SLOTS;
                 const int s = i % STAGES;
                 const uint32_t use = i / STAGES;
-                if (!mbar_wait(smem_u32(&tma_full[s]), use & 1)) {
+                // the int8 tile must have landed, and the MMAs that read the f16 slot last time must be done
+                if (!mbar_wait(smem_u32(&raw_full[r]), use_r & 1) ||
+                    (use >= 1 && !mbar_wait(smem_u32(&slot_free[s]), (use - 1) & 1))) {
                     report_timeout(p.status, kKernelPrefill, 4);
                     ok = false;
                     break;
                 }
-                const uint32_t raw = raw_addr(s), wf = wf_addr(s);
+                const uint32_t raw = raw_addr(r), wf = wf_addr(s);
+                uint4 v[BK / CONV_ROWS];
+#pragma unroll
+                for (int pass = 0; pass < BK / CONV_ROWS; ++pass) v[pass] = lds128(raw + (pass * CONV_ROWS + rb) * 128 + ci * 16);
+                __syncwarp();
+                if (lane == 0) mbar_arrive(smem_u32(&raw_empty[r]));  // the int8 tile is in registers
 #pragma unroll
                 for (int pass = 0; pass < BK / CONV_ROWS; ++pass) {
                     const int k = pass * CONV_ROWS + rb;
-                    const uint4 v = lds128(raw + k * 128 + ci * 16);
                     uint32_t h[8];
-                    cvt_s8x4_to_f16_pairs(v.x, h[0], h[1]);
-                    cvt_s8x4_to_f16_pairs(v.y, h[2], h[3]);
-                    cvt_s8x4_to_f16_pairs(v.z, h[4], h[5]);
-                    cvt_s8x4_to_f16_pairs(v.w, h[6], h[7]);
+                    cvt_s8x4_to_f16_pairs(v[pass].x, h[0], h[1]);
+                    cvt_s8x4_to_f16_pairs(v[pass].y, h[2], h[3]);
+                    cvt_s8x4_to_f16_pairs(v[pass].z, h[4], h[5]);
+                    cvt_s8x4_to_f16_pairs(v[pass].w, h[6], h[7]);
                     const uint32_t row = wf + (k >> 3) * 1024 + (k & 7) * 128;
                     const uint32_t a_first = row + (c_first >> 3) * 8192 + (((c_first & 7) ^ (k & 7)) << 4);
                     const uint32_t a_second = row + (c_second >> 3) * 8192 + (((c_second & 7) ^ (k & 7)) << 4);
@@ -278,7 +321,15 @@ __global__ void __launch_bounds__(THREADS, 1) qlinear_prefill_kn_kernel(const __
         }
     } else if (warp < 4) {
         // ---------------- epilogue ----------------
-        const int q = warp;  // TMEM lanes 32 q .. 32 q + 31
+        // Per 32 activation rows: each warp reads its 32 weight columns x 32 rows from tensor memory
+        // (one column per lane), scales, rounds and transposes them through the staging buffer; then the
+        // four warps together write the 32 x 128 block row by row with 16-byte stores, 256 contiguous bytes
+        // per row, to every destination.
+        const int q = warp;       // TMEM lanes 32 q .. 32 q + 31
+        const int et = threadIdx.x;  // 0 .. 127
+        unsigned char *staging = smem_gen + STAGING_OFF;
+        const int chunk = et & 15;   // 16-byte piece of a 256-byte output row
+        const int row_in_pass = et >> 4;
         uint32_t t_iter = 0;
         for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x, ++t_iter) {
             const int n0 = (tile % p.n_tiles) * TN;
@@ -290,28 +341,32 @@ __global__ void __launch_bounds__(THREADS, 1) qlinear_prefill_kn_kernel(const __
             }
             tc_fence_after_sync();
             const int n = n0 + 32 * q + lane;
-            const bool n_ok = n < p.N;
-            const float sc = n_ok ? __half2float(p.scale[n]) : 0.0f;
-            const size_t dst_off = (size_t)m0 * p.out.ldc + p.out.col0 + n;
+            const float sc = n < p.N ? __half2float(p.scale[n]) : 0.0f;
             const int m_left = p.M - m0;
+            const bool cols_ok = n0 + chunk * 8 < p.N;  // N is a multiple of 16: eight columns are in or out together
+            const size_t col_off = (size_t)p.out.col0 + n0 + chunk * 8;
 #pragma unroll 1
             for (int cb = 0; cb < TM / 32; ++cb) {
+                if (cb * 32 >= m_left) break;  // rows beyond M: nothing to store (uniform across the four warps)
                 uint32_t v[32];
                 tmem_ld_32x32(tmem_base + ((uint32_t)(32 * q) << 16) + buf * TM + cb * 32, v);
                 tmem_ld_wait();
-                if (n_ok) {
-                    __half h[32];
+                __half *col = reinterpret_cast<__half *>(staging) + 32 * q + lane;
 #pragma unroll
-                    for (int j = 0; j < 32; ++j) h[j] = __float2half_rn(__uint_as_float(v[j]) * sc);
+                for (int j = 0; j < 32; ++j) col[j * (STAGE_ROW_BYTES / 2)] = __float2half_rn(__uint_as_float(v[j]) * sc);
+                asm volatile("bar.sync 1, 128;" ::: "memory");  // the four epilogue warps: block complete
+#pragma unroll
+                for (int pass = 0; pass < 4; ++pass) {
+                    const int r = pass * 8 + row_in_pass;
+                    const int m = cb * 32 + r;
+                    if (m < m_left && cols_ok) {
+                        const uint4 val = *reinterpret_cast<const uint4 *>(staging + r * STAGE_ROW_BYTES + chunk * 16);
+                        const size_t off = (size_t)(m0 + m) * p.out.ldc + col_off;
 #pragma unroll 1
-                    for (int t = 0; t < p.out.count; ++t) {
-                        __half *dst = static_cast<__half *>(p.out.ptr[t]) + dst_off + (size_t)(cb * 32) * p.out.ldc;
-#pragma unroll
-                        for (int j = 0; j < 32; ++j) {
-                            if (cb * 32 + j < m_left) dst[(size_t)j * p.out.ldc] = h[j];
-                        }
+                        for (int t = 0; t < p.out.count; ++t) *reinterpret_cast<uint4 *>(static_cast<__half *>(p.out.ptr[t]) + off) = val;
                     }
                 }
+                asm volatile("bar.sync 1, 128;" ::: "memory");  // staging may be overwritten
             }
             tc_fence_before_sync();
             __syncwarp();
@@ -324,7 +379,7 @@ __global__ void __launch_bounds__(THREADS, 1) qlinear_prefill_kn_kernel(const __
     __syncthreads();
     if (warp == MMA_WARP) {
         tc_fence_after_sync();
-        tmem_dealloc(tmem_base, TMEM_COLS);
+        tmem_dealloc(tmem_base, Cfg::TMEM_COLS);
     }
 }
 
@@ -335,9 +390,31 @@ bool prefill_kn_supported(const void *a, const void *wq, int64_t N, int64_t K) {
            ((reinterpret_cast<uintptr_t>(wq) & 15u) == 0);
 }
 
-int launch_prefill_kn(const void *a, const void *wq, const void *scale, void *c, int64_t M, int64_t N, int64_t K,
-                      cudaStream_t stream, const OutTargets *targets) {
+// Height of the activation tile: 256 rows unless 64 rows fill more of
+// the machine.  Cost model: waves of tiles over the SMs times the time of one tile, where the shorter
+// tiles run the tensor core below its rate (more shared-memory traffic per flop).
+static int choose_tile_m(int64_t M, int64_t N, int sms) {
+    const int64_t n_tiles = ceil_div(N, prefill::TN);
+    const int cand[2] = {256, 64};
+    const double cost_per_row[2] = {1.0, 1.0 / 0.5};
+    int best = 256;
+    double best_cost = 0.0;
+    for (int i = 0; i < 2; ++i) {
+        const int64_t tiles = n_tiles * ceil_div(M, cand[i]);
+        const double cost = (double)ceil_div(tiles, sms) * cand[i] * cost_per_row[i];
+        if (i == 0 || cost < best_cost * 0.98) {
+            best = cand[i];
+            best_cost = cost;
+        }
+    }
+    return best;
+}
+
+template <int TM>
+static int launch_prefill_tm(const void *a, const void *wq, const void *scale, void *c, int64_t M, int64_t N, int64_t K,
+                             cudaStream_t stream, const OutTargets *targets, int sms) {
     using namespace prefill;
+    using Cfg = Config<TM>;
     CUtensorMap map_w, map_a;
     int rc = make_tensor_map_2d(&map_w, CU_TENSOR_MAP_DATA_TYPE_UINT8, wq, (uint64_t)N, (uint64_t)K, (uint64_t)N, TN, BK,
                                 CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B);
@@ -356,6 +433,10 @@ int launch_prefill_kn(const void *a, const void *wq, const void *scale, void *c,
         p.out.ldc = N;
         p.out.col0 = 0;
     }
+    for (int i = 0; i < p.out.count; ++i) {
+        if ((reinterpret_cast<uintptr_t>(p.out.ptr[i]) & 15u) != 0) return set_error(B200Q_INVALID_ARGUMENT, "qlinear: output %d is not 16-byte aligned", i);
+    }
+    if (p.out.ldc % 8 != 0 || p.out.col0 % 8 != 0) return set_error(B200Q_INVALID_ARGUMENT, "qlinear: output row length and column offset must be multiples of 8 elements");
     p.status = device_status_word();
     p.M = (int)M;
     p.N = (int)N;
@@ -364,20 +445,28 @@ int launch_prefill_kn(const void *a, const void *wq, const void *scale, void *c,
     p.m_tiles = (int)ceil_div(M, TM);
     const int64_t total = (int64_t)p.n_tiles * p.m_tiles;
     if (total > 2147483647LL) return set_error(B200Q_UNSUPPORTED, "qlinear: problem too large for the tile counter");
-    int sms = sm_count();
-    if (sms <= 0) sms = 148;
     const unsigned grid = (unsigned)(total < sms ? total : sms);
 
-    static bool attr_set[64] = {false};  // per device; a repeated set is harmless
+    static bool attr_set[64] = {false};  // per device and instantiation; a repeated set is harmless
     int dev = 0;
     B200Q_CUDA_TRY(cudaGetDevice(&dev));
     if (dev < 0 || dev >= 64 || !attr_set[dev]) {
-        B200Q_CUDA_TRY(cudaFuncSetAttribute(qlinear_prefill_kn_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
+        B200Q_CUDA_TRY(cudaFuncSetAttribute(qlinear_prefill_kn_kernel<TM>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES));
         if (dev >= 0 && dev < 64) attr_set[dev] = true;
     }
-    qlinear_prefill_kn_kernel<<<grid, THREADS, SMEM_BYTES, stream>>>(map_w, map_a, p);
+    qlinear_prefill_kn_kernel<TM><<<grid, THREADS, Cfg::SMEM_BYTES, stream>>>(map_w, map_a, p);
     B200Q_CHECK_LAUNCH("qlinear_prefill_kn_kernel");
     return B200Q_OK;
+}
+
+int launch_prefill_kn(const void *a, const void *wq, const void *scale, void *c, int64_t M, int64_t N, int64_t K,
+                      cudaStream_t stream, const OutTargets *targets) {
+    int sms = sm_count();
+    if (sms <= 0) sms = 148;
+    switch (choose_tile_m(M, N, sms)) {
+        case 64: return launch_prefill_tm<64>(a, wq, scale, c, M, N, K, stream, targets, sms);
+        default: return launch_prefill_tm<256>(a, wq, scale, c, M, N, K, stream, targets, sms);
+    }
 }
 
 }  // namespace b200q

@@ -69,7 +69,7 @@ B200Q_API int b200q_qlinear_f16_i8_static(const void *a, const void *wq, const v
         return set_error(B200Q_UNSUPPORTED, "qlinear_f16_i8_static: operands need 16-byte aligned bases and rows (N %% 16 == 0, K %% 8 == 0); "
                                             "got N=%lld K=%lld", (long long)N, (long long)K);
     }
-    if (M >= kPrefillMinM) return launch_prefill_kn(a, wq, scale, c, M, N, K, s);  // needs no scratch at all
+    if (use_prefill_kernel(M, N, K)) return launch_prefill_kn(a, wq, scale, c, M, N, K, s);  // needs no scratch at all
 
     const DecodePlan plan = plan_decode(M, N, K);
     const size_t need = plan.counter_bytes + plan.partial_bytes;

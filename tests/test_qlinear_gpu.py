@@ -64,7 +64,8 @@ def test_qlinear_reference_test_shapes(shape_a, shape_w):
     assert np.allclose(c.float().cpu().numpy(), want, atol=2e-1, rtol=2e-1)
 
 
-@pytest.mark.parametrize('m,k,n', [(17, 512, 256), (64, 1024, 512), (200, 640, 384), (256, 4096, 1024)])
+@pytest.mark.parametrize('m,k,n', [(17, 512, 256), (64, 1024, 512), (200, 640, 384), (256, 4096, 1024), (33, 64, 16), (100, 72, 4096),
+                                   (300, 1024, 2048), (513, 512, 19008), (1000, 264, 272)])
 def test_qlinear_larger_m(m, k, n):
     wq, scale = _quantized(k, n, seed=5)
     a = seeded_activation(m, k, seed=6)
