@@ -7,6 +7,7 @@ nor the library.
 """
 from . import ffi
 from . import quant
+from . import graph
 from .quant import (
     symmetric_quantize,
     symmetric_dequantize,

@@ -1,0 +1,39 @@
+"""torch.compile backend: ``torch.compile(model, backend='hidet_b200', options={'precision': 'int8'})``.
+
+The reference's backend (python/hidet/graph/frontend/torch/dynamo_backends.py:144-175) opens a fresh
+PassContext and offers no way to switch quantization on; this backend takes it as an option.  The fx
+graph is rewritten by the quantization pass (float16 linear layers with constant weights become
+calls into libhidet_b200q.so) and otherwise runs as captured: only the quantized-linear path is
+replaced.  Weights are frozen at compile time, as the reference freezes them into graph constants.
+"""
+from __future__ import annotations
+
+from typing import Any, Dict, List, Optional
+
+import torch
+import torch.fx as fx
+
+from .transforms import PassContext, optimize
+
+_registered = False
+
+
+def hidet_b200_backend(gm: fx.GraphModule, example_inputs: List[Any], options: Optional[Dict[str, Any]] = None, **kwargs):
+    options = dict(options or {})
+    options.update(kwargs.get('options') or {})
+    precision = options.get('precision', 'int8')
+    with PassContext() as ctx:
+        ctx.set_precision(precision)
+        optimize(gm, example_inputs)
+    return gm.forward
+
+
+def register() -> None:
+    """Makes backend='hidet_b200' known to torch.compile (idempotent)."""
+    global _registered
+    if _registered:
+        return
+    from torch._dynamo import register_backend
+
+    register_backend(name='hidet_b200', compiler_fn=hidet_b200_backend)
+    _registered = True

@@ -1,0 +1,152 @@
+"""Operator objects, the quantization pass over fx graphs and the torch.compile backend on the GPU."""
+import numpy as np
+import pytest
+import torch
+import torch.fx as fx
+import torch.nn as nn
+import torch.nn.functional as F
+
+import hidet_b200
+from hidet_b200 import graph as hg
+
+pytestmark = pytest.mark.gpu
+
+
+def test_operator_objects_follow_the_reference_contract():
+    g = torch.Generator().manual_seed(0)
+    w = (torch.randn(256, 128, generator=g) * 0.02).half().cuda()
+    op = hg.SymmetricQuantizationOp(w, quant_type='int8', dims=0)
+    wq, scale = op.outputs
+    assert op.attrs == {'dims': 0, 'quant_type': 'int8'} and op.name == 'SymmetricQuantization'
+    wq2, scale2 = op.reforward([w])                      # cls(*inputs, **attrs)
+    assert torch.equal(wq, wq2) and torch.equal(scale, scale2)
+    wd = hg.SymmetricDeQuantizationOp(wq, scale, dims=0).outputs[0]
+    assert torch.allclose(wd.float(), w.float(), atol=1e-1, rtol=1e-1)
+    a = torch.randn(4, 256, generator=g).half().cuda()
+    c = hg.SymmetricQuantizedMatmulOp(a, wq, scale).outputs[0]
+    assert torch.equal(c, hidet_b200.symmetric_quant_matmul(a, wq, scale))
+    parts = hg.SymmetricQuantizedMatmulF16I8Op(a, wq, scale, parallel_k_parts=3).outputs[0]
+    assert tuple(parts.shape) == (3, 4, 128)
+    with pytest.raises(ValueError):
+        hg.SymmetricQuantizedMatmulF16I8Op(a, wq, scale, parallel_k_parts=2.0)
+
+
+def test_later_resolve_rule_wins():
+    calls = []
+
+    @hg.register_resolve_rule(hg.SymmetricQuantizedMatmulOp)
+    class Probe(hg.ResolveRule):
+        def resolve(self, op):
+            calls.append(op)
+            return None  # fall through to the rule registered before
+
+    try:
+        a = torch.zeros(2, 64, dtype=torch.float16, device='cuda')
+        wq = torch.zeros(64, 32, dtype=torch.int8, device='cuda')
+        scale = torch.ones(32, dtype=torch.float16, device='cuda')
+        out = hg.SymmetricQuantizedMatmulOp(a, wq, scale).outputs[0]
+        assert len(calls) == 1 and tuple(out.shape) == (2, 32)
+    finally:
+        from hidet_b200.graph import transforms
+
+        transforms._resolve_rules[hg.SymmetricQuantizedMatmulOp].pop()
+
+
+class TwoLinears(nn.Module):
+    def __init__(self):
+        super().__init__()
+        g = torch.Generator().manual_seed(1)
+        self.w_kn = nn.Parameter((torch.randn(256, 512, generator=g) * 0.02).half())   # Hidet layout [K, N]
+        self.fc = nn.Linear(512, 128, bias=True)                                      # torch layout [N, K]
+        with torch.no_grad():
+            self.fc.weight.copy_(torch.randn(128, 512, generator=g) * 0.02)
+            self.fc.bias.copy_(torch.randn(128, generator=g) * 0.1)
+
+    def forward(self, x):
+        return self.fc(F.silu(torch.matmul(x, self.w_kn)))
+
+
+def test_quantization_pass_rewrites_matmul_and_linear():
+    model = TwoLinears().half().cuda().eval()
+    x = torch.randn(8, 256, generator=torch.Generator().manual_seed(2)).half().cuda()
+    want = model(x)
+    gm = fx.symbolic_trace(model)
+    with hg.PassContext() as ctx:
+        ctx.set_precision('int8')
+        hg.optimize(gm)
+    targets = [n.target for n in gm.graph.nodes if n.op == 'call_function']
+    assert targets.count(hg.quantized_matmul) == 2
+    assert torch.matmul not in targets and F.linear not in targets
+    assert not any(n.op == 'call_module' for n in gm.graph.nodes)
+    buffers = dict(gm.named_buffers())
+    assert buffers['_b200q_wq_0'].dtype == torch.int8 and tuple(buffers['_b200q_wq_0'].shape) == (256, 512)
+    assert tuple(buffers['_b200q_wq_1'].shape) == (512, 128)        # the [N, K] weight, transposed once
+    # per-output-channel scales of the nn.Linear weight: one per row of W[N, K]
+    wq_ref, scale_ref = hidet_b200.symmetric_quantize(model.fc.weight.detach().t().contiguous(), 'int8', dims=0)
+    assert torch.equal(buffers['_b200q_wq_1'], wq_ref) and torch.equal(buffers['_b200q_scale_1'], scale_ref)
+    got = gm(x)
+    # the reference's own acceptance for its quantized matmul against the fp16 one: atol = rtol = 2e-1
+    assert torch.allclose(got.float(), want.float(), atol=2e-1, rtol=2e-1)
+    # and exactly what the ops give when called by hand
+    h = F.silu(hidet_b200.symmetric_quant_matmul(x, buffers['_b200q_wq_0'], buffers['_b200q_scale_0']))
+    manual = hidet_b200.symmetric_quant_matmul(h, buffers['_b200q_wq_1'], buffers['_b200q_scale_1']) + model.fc.bias
+    assert torch.equal(got, manual)
+
+
+def test_pass_without_int8_leaves_the_graph_alone():
+    model = TwoLinears().half().cuda().eval()
+    gm = fx.symbolic_trace(model)
+    with hg.PassContext():
+        hg.optimize(gm)
+    assert not any(n.target is hg.quantized_matmul for n in gm.graph.nodes)
+
+
+class Block(nn.Module):
+    """One Llama-style decoder block: RMSNorm, attention with separate projections, SwiGLU."""
+
+    def __init__(self, hidden=256, heads=4, ffn=688):
+        super().__init__()
+        self.heads = heads
+        self.q = nn.Linear(hidden, hidden, bias=False)
+        self.k = nn.Linear(hidden, hidden, bias=False)
+        self.v = nn.Linear(hidden, hidden, bias=False)
+        self.o = nn.Linear(hidden, hidden, bias=False)
+        self.gate = nn.Linear(hidden, ffn, bias=False)
+        self.up = nn.Linear(hidden, ffn, bias=False)
+        self.down = nn.Linear(ffn, hidden, bias=False)
+        self.n1 = nn.Parameter(torch.ones(hidden))
+        self.n2 = nn.Parameter(torch.ones(hidden))
+        for p in self.parameters():
+            if p.dim() == 2:
+                nn.init.normal_(p, std=0.02)
+
+    @staticmethod
+    def rms(x, w):
+        return (x.float() * torch.rsqrt(x.float().pow(2).mean(-1, keepdim=True) + 1e-5)).to(x.dtype) * w
+
+    def forward(self, x):
+        b, t, h = x.shape
+        y = self.rms(x, self.n1)
+        q, k, v = (f(y).view(b, t, self.heads, h // self.heads).transpose(1, 2) for f in (self.q, self.k, self.v))
+        a = F.scaled_dot_product_attention(q, k, v, is_causal=True).transpose(1, 2).reshape(b, t, h)
+        x = x + self.o(a)
+        y = self.rms(x, self.n2)
+        return x + self.down(F.silu(self.gate(y)) * self.up(y))
+
+
+def test_torch_compile_backend_quantizes_a_decoder_block():
+    hg.register()
+    torch.manual_seed(3)
+    model = Block().half().cuda().eval()
+    x = torch.randn(1, 24, 256, device='cuda').half()
+    with torch.no_grad():
+        want = model(x)
+        compiled = torch.compile(model, backend='hidet_b200', options={'precision': 'int8'})
+        got = compiled(x)
+        again = compiled(x)
+    assert torch.equal(got, again)
+    # the reference's acceptance for its int8 model test: atol = rtol = 0.5 (tests/models/test_quant_gpt2.py:103)
+    assert torch.allclose(got.float(), want.float(), atol=0.5, rtol=0.5)
+    assert (got.float() - want.float()).abs().max() < 5e-2
+    # the weights really went through the quantized kernels: int8 codes differ from fp16 weights' output
+    assert not torch.equal(got, want)
