@@ -8,6 +8,7 @@ nor the library.
 from . import ffi
 from . import quant
 from . import graph
+from .cuda_graph import CudaGraph
 from .quant import (
     symmetric_quantize,
     symmetric_dequantize,

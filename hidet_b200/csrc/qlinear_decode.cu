@@ -50,7 +50,7 @@ constexpr int THREADS = 32 * (CONSUMER_WARPS + 1);
 constexpr int W_STAGE_BYTES = BK * BN;       // 8192
 constexpr int A_STAGE_BYTES = BM * BK * 2;   // 2048
 constexpr int PIPE_BYTES = STAGES * (W_STAGE_BYTES + A_STAGE_BYTES);
-constexpr int RECV_BYTES = BM * BN * 4;      // partial tiles pushed by the CTAs of the cluster: [rank][row][BN / ranks] fp32
+constexpr int RECV_BYTES = BM * (BN + 8) * 4; // partial tiles pushed by the CTAs of the cluster: [rank][row][ceil(BN / ranks)] fp32
 constexpr int SMEM_BYTES = PIPE_BYTES + RECV_BYTES + 1024;  // + alignment slack
 constexpr int kCtasPerSm = 4;                // resident CTAs per SM the plan aims at
 constexpr int64_t kMaxCounters = 65536;      // arrival counters at the head of the workspace
@@ -320,7 +320,7 @@ __global__ void __launch_bounds__(THREADS) qlinear_decode_kn_kernel(const __grid
     // (Without a cluster the CTA is its own owner and the same code runs on local shared memory.)
     const uint32_t nranks = cluster_nctarank();
     const uint32_t rank = cluster_ctarank();
-    const int cols_per = BN / (int)nranks;  // 128 ... 16 columns per owner
+    const int cols_per = (BN + (int)nranks - 1) / (int)nranks;  // columns per owner (the last owner may have fewer)
     cluster_wait_acquire();                 // every CTA of the cluster is running
     if (consumer) {
 #pragma unroll
@@ -349,7 +349,7 @@ __global__ void __launch_bounds__(THREADS) qlinear_decode_kn_kernel(const __grid
             const int r = idx / cols_per;
             const int cc = idx - r * cols_per;
             const int nn = col_first + cc;
-            if (nn < p.N) {
+            if (nn < p.N && (int)rank * cols_per + cc < BN) {
                 float v = 0.0f;
                 for (uint32_t jr = 0; jr < nranks; ++jr) v += recv[((int)jr * BM + r) * cols_per + cc];
                 store_out(p.out, m0 + r, nn, __float2half_rn(v * __half2float(p.scale[nn])));
@@ -367,7 +367,7 @@ __global__ void __launch_bounds__(THREADS) qlinear_decode_kn_kernel(const __grid
         const int r = idx / cols_per;
         const int cc = idx - r * cols_per;
         const int nn = col_first + cc;
-        if (nn < p.N) {
+        if (nn < p.N && (int)rank * cols_per + cc < BN) {
             float v = 0.0f;
             for (uint32_t jr = 0; jr < nranks; ++jr) v += recv[((int)jr * BM + r) * cols_per + cc];
             __stcg(&p.partial[((size_t)group * p.M + (m0 + r)) * p.N + nn], v);
@@ -387,7 +387,7 @@ __global__ void __launch_bounds__(THREADS) qlinear_decode_kn_kernel(const __grid
         const int r = idx / cols_per;
         const int cc = idx - r * cols_per;
         const int nn = col_first + cc;
-        if (nn < p.N) {
+        if (nn < p.N && (int)rank * cols_per + cc < BN) {
             float v = 0.0f;
 #pragma unroll 4
             for (int gr = 0; gr < p.groups; ++gr) v += __ldcg(&p.partial[((size_t)gr * p.M + (m0 + r)) * p.N + nn]);
@@ -416,10 +416,10 @@ DecodePlan plan_decode(int64_t M, int64_t N, int64_t K) {
     if (splits > max_splits) splits = max_splits;
     if (splits > 64) splits = 64;
     if (splits < 1) splits = 1;
-    // The splits of a tile form clusters (partials meet in distributed shared memory); more splits
-    // than a cluster holds become several clusters per tile that meet in the workspace.
-    int c = 1;
-    while (c * 2 <= splits && c * 2 <= kMaxCluster) c *= 2;
+    // The splits of a tile form clusters of up to eight CTAs (partials meet in distributed shared
+    // memory); more splits than a cluster holds become several full clusters per tile that meet in the
+    // workspace.
+    int c = (int)(splits < kMaxCluster ? splits : kMaxCluster);
     int groups = (int)(splits / c);
     if (groups < 1 || tiles * c > kMaxCounters) groups = 1;
     pl.cluster = c;
