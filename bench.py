@@ -264,20 +264,10 @@ def extra_sections(torch, hidet_b200, device, stream, peaks):
         for w in ws:
             hidet_b200.symmetric_quantize(w, 'int8', dims=0)
 
-    # quantize allocates its outputs, which a graph capture cannot do: time eager launches with events
-    qfn()
-    stream.synchronize()
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    e0.record(stream)
-    reps = 10
-    for _ in range(reps):
-        qfn()
-    e1.record(stream)
-    stream.synchronize()
-    us = e0.elapsed_time(e1) * 1e3 / (reps * len(ws))
+    us = time_graph(torch, stream, qfn, len(ws))  # outputs come from the graph's private pool
     qbytes = 3 * k * n + 2 * n
     out['quantize'] = {'K': k, 'N': n, 'dtype': 'f16->i8, dims=0', 'us_per_launch': round(us, 2), 'GBps': round(qbytes / us / 1e3, 1),
-                       'frac_of_hbm_peak': round(qbytes / us / 1e3 / peaks['hbm_gbs'], 4), 'timing': 'eager launches'}
+                       'frac_of_hbm_peak': round(qbytes / us / 1e3 / peaks['hbm_gbs'], 4)}
     return out
 
 

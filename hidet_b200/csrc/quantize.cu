@@ -43,9 +43,36 @@ struct Arith<__half> {
     static __device__ __forceinline__ __half max_(__half a, __half b) { return __hmax(a, b); }
     static __device__ __forceinline__ __half div_(__half a, __half b) { return a / b; }
     static __device__ __forceinline__ __half qmax(int q) { return (__half)(float)q; }
+    // w / scale for many w and one scale.  CUDA's __half division (cuda_fp16.hpp, __hdiv) converts both
+    // operands to f32, takes rcp.approx.ftz.f32 of the divisor, multiplies, rounds to half, and redoes
+    // the last steps with one correction when the result is a non-zero value below 0x008F.  The
+    // reciprocal depends on the divisor only, so it is taken once per scale; every other operation is
+    // the same one, in the same order, which keeps the quotient bit-identical to `w / scale`.
+    struct Divisor {
+        float fb;
+        float rcp;
+    };
+    static __device__ __forceinline__ Divisor prepare(__half scale) {
+        Divisor d;
+        d.fb = __half2float(scale);
+        asm("{rcp.approx.ftz.f32 %0, %1;\n}" : "=f"(d.rcp) : "f"(d.fb));
+        return d;
+    }
+    static __device__ __forceinline__ __half div_prepared(__half a, const Divisor &d) {
+        const float fa = __half2float(a);
+        float fv = d.rcp * fa;
+        __half v = __float2half(fv);
+        const __half av = __habs(v);
+        if (__hlt(av, __ushort_as_half((unsigned short)0x008FU)) && __hlt(__float2half(0.0f), av)) {
+            const float err = __fmaf_rn(-d.fb, fv, fa);
+            fv = __fmaf_rn(d.rcp, err, fv);
+            v = __float2half(fv);
+        }
+        return v;
+    }
     template <typename Q>
-    static __device__ __forceinline__ Q quant(__half w, __half scale) {
-        return (Q)(short)(hrint(w / scale));
+    static __device__ __forceinline__ Q quant(__half w, const Divisor &d) {
+        return (Q)(short)(hrint(div_prepared(w, d)));
     }
     template <typename Q>
     static __device__ __forceinline__ __half dequant(Q q, __half scale) {
@@ -60,6 +87,8 @@ struct Arith<__nv_bfloat16> {
     static __device__ __forceinline__ __nv_bfloat16 max_(__nv_bfloat16 a, __nv_bfloat16 b) { return __hmax(a, b); }
     static __device__ __forceinline__ __nv_bfloat16 div_(__nv_bfloat16 a, __nv_bfloat16 b) { return a / b; }
     static __device__ __forceinline__ __nv_bfloat16 qmax(int q) { return (__nv_bfloat16)(float)q; }
+    typedef __nv_bfloat16 Divisor;
+    static __device__ __forceinline__ Divisor prepare(__nv_bfloat16 scale) { return scale; }
     template <typename Q>
     static __device__ __forceinline__ Q quant(__nv_bfloat16 w, __nv_bfloat16 scale) {
         return (Q)(hrint(w / scale));
@@ -77,6 +106,8 @@ struct Arith<float> {
     static __device__ __forceinline__ float max_(float a, float b) { return fmaxf(a, b); }
     static __device__ __forceinline__ float div_(float a, float b) { return a / b; }
     static __device__ __forceinline__ float qmax(int q) { return (float)q; }
+    typedef float Divisor;
+    static __device__ __forceinline__ Divisor prepare(float scale) { return scale; }
     template <typename Q>
     static __device__ __forceinline__ Q quant(float w, float scale) {
         return (Q)(roundf(w / scale));
@@ -190,9 +221,9 @@ __global__ void __launch_bounds__(kThreads) quantize_cols_kernel(const T *__rest
         if (c < cols) scale[c] = A::div_(amax_s[threadIdx.x], qm);
     }
     if (col_ok) {
-        T s[VEC];
+        typename A::Divisor s[VEC];
 #pragma unroll
-        for (int i = 0; i < VEC; ++i) s[i] = A::div_(amax_s[tx * VEC + i], qm);
+        for (int i = 0; i < VEC; ++i) s[i] = A::prepare(A::div_(amax_s[tx * VEC + i], qm));
         const T *src = w + row0 * cols + col;
         Q *dst = wq + row0 * cols + col;
 #pragma unroll 4
@@ -258,8 +289,9 @@ __global__ void __launch_bounds__(kThreads) quantize_rows_kernel(const T *__rest
         if (threadIdx.x == 0) amax_s = a;
     }
     __syncthreads();
-    const T s = A::div_(amax_s, A::qmax(QMax<Q>::value));
-    if (threadIdx.x == 0) scale[row] = s;
+    const T s_val = A::div_(amax_s, A::qmax(QMax<Q>::value));
+    if (threadIdx.x == 0) scale[row] = s_val;
+    const typename A::Divisor s = A::prepare(s_val);
 
 #pragma unroll
     for (int j = 0; j < REG_CHUNKS; ++j) {
