@@ -23,28 +23,16 @@
 // Replaces the generated mma.sync kernel of python/hidet/graph/ops/quant/matmul_f16_i8.py:136-485
 // (f16 accumulation, 64x128 tiles, no split-K by default) for M <= 16, and serves larger M by
 // tiling M over blockIdx.z.
-#include <cstdlib>
-
 #include "common.cuh"
 #include "qlinear.h"
 
 namespace b200q {
-#ifdef B200Q_TRACE
-unsigned long long *g_trace = nullptr;
-__device__ __forceinline__ unsigned long long gtime() { unsigned long long t; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t)); return t; }
-#define TRACE(slot) do { if (p.trace && threadIdx.x == 0) p.trace[((blockIdx.z * gridDim.y + blockIdx.y) * gridDim.x + blockIdx.x) % 8192 * 8 + (slot)] = gtime(); } while (0)
-#else
-#define TRACE(slot) do {} while (0)
-#endif
 namespace decode {
 
 constexpr int BN = 128;                      // columns per CTA
 constexpr int BK = 64;                       // k rows per pipeline stage
 constexpr int BM = 16;                       // activation rows per CTA
-#ifndef B200Q_DECODE_STAGES
-#define B200Q_DECODE_STAGES 4
-#endif
-constexpr int STAGES = B200Q_DECODE_STAGES;
+constexpr int STAGES = 4;
 constexpr int CONSUMER_WARPS = 4;            // each owns BN / 4 = 32 columns
 constexpr int THREADS = 32 * (CONSUMER_WARPS + 1);
 constexpr int W_STAGE_BYTES = BK * BN;       // 8192
@@ -139,10 +127,6 @@ struct Params {
     int iters_per_split;      // BK-sized k steps per split
     int groups;               // clusters per output tile (splits = groups * cluster size)
     int mode;                 // kModeDirect or kModeSplit
-#ifdef B200Q_TRACE
-    unsigned long long *trace;
-    int skip_compute;
-#endif
 };
 
 // MT: 8-row blocks of activations per CTA (1: up to 8 rows, 2: up to 16).
@@ -175,8 +159,6 @@ __global__ void __launch_bounds__(THREADS) qlinear_decode_kn_kernel(const __grid
     int n_iters = total_iters - it_begin;
     if (n_iters > p.iters_per_split) n_iters = p.iters_per_split;
     if (n_iters < 0) n_iters = 0;
-
-    TRACE(0);
     if (threadIdx.x == 0) {
 #pragma unroll
         for (int s = 0; s < STAGES; ++s) {
@@ -251,10 +233,6 @@ __global__ void __launch_bounds__(THREADS) qlinear_decode_kn_kernel(const __grid
                 report_timeout(p.status, kKernelDecode, 2);
                 break;
             }
-            if (it == 0) TRACE(1);
-#ifdef B200Q_TRACE
-            if (p.skip_compute) { __syncwarp(); if (lane == 0) mbar_arrive(smem_u32(&empty_bar[s])); continue; }
-#endif
             const uint32_t wb = w_base + s * W_STAGE_BYTES + off_w;
             const uint32_t ab = a_base + s * A_STAGE_BYTES + off_a;
             uint32_t q[4][4];
@@ -282,7 +260,6 @@ __global__ void __launch_bounds__(THREADS) qlinear_decode_kn_kernel(const __grid
             }
         }
     }
-    TRACE(2);
     pdl_launch_dependents();  // the next kernel may start streaming its weight
 
     int rows = p.M - m0;
@@ -342,7 +319,6 @@ __global__ void __launch_bounds__(THREADS) qlinear_decode_kn_kernel(const __grid
     }
     cluster_arrive_release();
     cluster_wait_acquire();  // all partial tiles of this CTA's columns have landed
-    TRACE(3);
     const int col_first = n0 + (int)rank * cols_per;  // first column this CTA owns
     if (p.groups == 1) {
         for (int idx = threadIdx.x; idx < rows * cols_per; idx += THREADS) {
@@ -355,7 +331,6 @@ __global__ void __launch_bounds__(THREADS) qlinear_decode_kn_kernel(const __grid
                 store_out(p.out, m0 + r, nn, __float2half_rn(v * __half2float(p.scale[nn])));
             }
         }
-        TRACE(4);
         return;
     }
 
@@ -485,10 +460,6 @@ int launch_decode_kn(const void *a, const void *wq, const void *scale, void *c, 
     p.iters_per_split = pl.iters_per_split;
     p.groups = pl.groups;
     p.mode = pl.splits == 1 ? kModeDirect : kModeSplit;
-#ifdef B200Q_TRACE
-    p.trace = g_trace;
-    p.skip_compute = getenv("B200Q_SKIP") ? atoi(getenv("B200Q_SKIP")) : 0;
-#endif
 
     auto kernel = (M - (int64_t)(pl.m_tiles - 1) * BM <= 8 && pl.m_tiles == 1) ? qlinear_decode_kn_kernel<1> : qlinear_decode_kn_kernel<2>;
     static bool attr_set[64] = {false};  // per device; a repeated set is harmless
