@@ -40,6 +40,9 @@ def run_sharded(args) -> int:
 
     peaks = measured_peaks()
     k, n = K_70B, N_70B
+    global MS_70B
+    if getattr(args, 'm_list', None):
+        MS_70B = tuple(int(x) for x in args.m_list.split(','))
     begin, end = column_range(n, rank, world)
     n_local = end - begin
     copies = max(2, -(-(2 * 128 * 1024 * 1024) // (k * n_local)))
@@ -163,7 +166,7 @@ def run_sharded(args) -> int:
             'metric': 'quant-linear HBM GB/s (70B-shaped layer, column-parallel)', 'value': value, 'unit': 'GB/s', 'n_gpus': world,
             'steps': args.steps, 'warmup': max(args.warmup, 3), 'ms_per_step': ms_per_step, 'higher_is_better': True,
             'scaling': 'strong', 'vs_baseline': None, 'dtype': 'f16', 'accumulate': 'f32', 'weight_dtype': 'i8', 'data': 'synthetic',
-            'config': {'workload': 'sharded-70b-layer', 'K': k, 'N': n, 'M': list(MS_70B), 'parallelism': 'tp{} (columns), outputs by {}'.format(world, 'peer stores from the epilogue + barrier' if args.gather == 'p2p' else 'NCCL all-gather'),
+            'config': {'workload': 'sharded-70b-layer', 'K': k, 'N': n, 'M': list(MS_70B), 'parallelism': 'tp{} (columns), outputs by {}'.format(world, 'peer stores from the epilogue (M <= 32) or peer copies after the kernel, + barrier' if args.gather == 'p2p' else 'NCCL all-gather'),
                        'weights_in_rotation': copies, 'l2': 'inputs larger than L2: {} distinct weight shards of {} MB per rank'.format(copies, k * n_local // 1000000),
                        'timing': timing + ', CUDA events, barrier on both sides, max over ranks'},
             'tflops': flops_per_step / (ms_per_step * 1e-3) / 1e12,
@@ -171,7 +174,7 @@ def run_sharded(args) -> int:
             'clocks': clocks.summary(),
             'roofline': {'bound': 'hbm for M <= 16, tensor for M >= 256', 'achieved': value, 'peak': peaks['hbm_gbs'] * world, 'unit': 'GB/s',
                          'frac': value / (peaks['hbm_gbs'] * world), 'traffic': None, 'peak_source': peaks['source'] + ' (burst copy) x n_gpus',
-                         'kernel': 'qlinear_decode_kn_kernel / qlinear_prefill_kn_kernel + ncclAllGather'},
+                         'kernel': 'qlinear_decode_kn_kernel / qlinear_prefill_kn_kernel' + (' + ncclAllGather' if args.gather == 'nccl' else ' + peer copies')},
             'shapes': shapes,
             'e2e': {'value': e2e_value, 'unit': 'GB/s', 'h2d_bytes_per_step': sum(t.numel() * 2 for t in pinned_in.values()),
                     'd2h_bytes_per_step': sum(t.numel() * 2 for t in pinned_out.values()), 'ms_per_step': e2e_ms},

@@ -133,10 +133,24 @@ B200Q_API int b200q_qlinear_f16_i8_parts(const void *a, const void *wq, const vo
  * python/hidet/graph/ops/distributed.py:63-97 (whose result is rank-major and needs a reshuffle).
  * The caller orders the ranks afterwards (a barrier between "all kernels done" and "outputs read").
  * `dst` is a host array.  KN layout; workspace as for b200q_qlinear_f16_i8 with the same M, N, K.
+ * Several destinations are served for M <= 32 (the small-M kernel); for larger M the call returns
+ * B200Q_UNSUPPORTED unless n_dst == 1: run it into this rank's own buffer and copy the columns on.
  */
 B200Q_API int b200q_qlinear_f16_i8_to_peers(const void *a, const void *wq, const void *scale, void *const *dst, int n_dst,
                                             int64_t ldc, int64_t col_offset, int64_t M, int64_t N, int64_t K, void *workspace,
                                             size_t workspace_bytes, void *stream);
+
+/*
+ * The second half of the column-parallel layer for large M: copies columns
+ * [col_offset, col_offset + cols) of the fp16 matrix src[rows, ld] into the same place of every
+ * dst[i][rows, ld] (pointers valid on this device, peer-mapped for other GPUs; an entry equal to src
+ * is skipped).  One strided device-to-device copy per destination, executed by the copy engines in
+ * stream order; `dst` is a host array.  With b200q_qlinear_f16_i8_to_peers(n_dst = 1) in front it
+ * takes the place of the all-gather op of python/hidet/graph/ops/distributed.py:63-97
+ * (ncclAllGather, python/hidet/ir/primitives/cuda/nccl.py:62-73).
+ */
+B200Q_API int b200q_push_columns(const void *src, void *const *dst, int n_dst, int64_t rows, int64_t cols, int64_t ld,
+                                 int64_t col_offset, void *stream);
 
 /*
  * Bytes of the scratch array built into the library for b200q_qlinear_f16_i8_static (512 KiB).

@@ -197,3 +197,39 @@ def test_qlinear_argument_checks_follow_the_reference():
         ffi.func('b200q_qlinear_f16_i8')(big_a.data_ptr(), big_w.data_ptr(), big_s.data_ptr(), out.data_ptr(), m, n, k, 0,
                                          tiny.data_ptr(), tiny.numel(), torch.cuda.current_stream().cuda_stream)
     assert ffi.func('b200q_check_status')() == ffi.OK
+
+
+def _to_destinations(a, wq, scale, dsts, ldc, col0):
+    import ctypes
+
+    from hidet_b200.runtime import workspaces
+
+    m, k = a.shape
+    n = wq.shape[1]
+    table = (ctypes.c_void_p * len(dsts))(*[d.data_ptr() for d in dsts])
+    ws_bytes = ffi.func('b200q_qlinear_workspace_bytes')(m, n, k, 0)
+    ws_ptr, ws_size = workspaces.get(a.device, ws_bytes)
+    ffi.func('b200q_qlinear_f16_i8_to_peers')(a.data_ptr(), wq.data_ptr(), scale.data_ptr(), table, len(dsts), ldc, col0, m, n, k,
+                                             ws_ptr, ws_size, torch.cuda.current_stream().cuda_stream)
+
+
+@pytest.mark.parametrize('m,k,n', [(1, 1024, 256), (16, 8192, 1792), (32, 512, 128), (300, 2048, 256), (40, 8192, 4096)])
+def test_qlinear_into_a_column_range_of_wider_outputs(m, k, n):
+    """The column-parallel entry point on one GPU: every destination gets the plain result in its columns and
+    nothing outside them; several destinations are for the small-M kernel only."""
+    wq, scale = _quantized(k, n, seed=5)
+    a = torch.from_numpy(seeded_activation(m, k, seed=6)).cuda()
+    wq_t, scale_t = torch.from_numpy(wq).cuda(), torch.from_numpy(scale).cuda()
+    want = hidet_b200.symmetric_quant_matmul(a, wq_t, scale_t)
+    ldc, col0 = 2 * n + 64, n + 32
+    count = 3 if m <= 32 else 1
+    dsts = [torch.full((m, ldc), -7.0, dtype=torch.float16, device='cuda') for _ in range(count)]
+    _to_destinations(a, wq_t, scale_t, dsts, ldc, col0)
+    torch.cuda.synchronize()
+    for d in dsts:
+        assert torch.equal(d[:, col0:col0 + n], want)
+        assert bool((d[:, :col0] == -7.0).all()) and bool((d[:, col0 + n:] == -7.0).all())
+    if m > 32:
+        with pytest.raises(ffi.BackendException, match='one destination'):
+            _to_destinations(a, wq_t, scale_t, dsts + dsts, ldc, col0)
+    assert ffi.func('b200q_check_status')() == ffi.OK
