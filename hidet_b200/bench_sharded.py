@@ -43,6 +43,11 @@ def run_sharded(args) -> int:
     global MS_70B
     if getattr(args, 'm_list', None):
         MS_70B = tuple(int(x) for x in args.m_list.split(','))
+    if args.gather is None:
+        # Peer stores and peer copies are the faster delivery and the default on two GPUs.  On four and
+        # eight GPUs runs of that path ended in a launch failure whose cause is not known, so there the
+        # default is the NCCL all-gather.
+        args.gather = 'p2p' if world <= 2 else 'nccl'
     begin, end = column_range(n, rank, world)
     n_local = end - begin
     copies = max(2, -(-(2 * 128 * 1024 * 1024) // (k * n_local)))
@@ -143,6 +148,38 @@ def run_sharded(args) -> int:
         us_local = timed(local_only, 5) * 1e3 / copies
         shapes[-1]['us_local_kernel'] = round(us_local, 2)
 
+    # The same layer, unsharded, on this GPU alone (every rank does it at once, without communication; rank 0's
+    # time is reported): what the sharded layer is to be compared with.
+    one_gpu = []
+    full_layers = []
+    for i in range(2):
+        gen = torch.Generator(device=device).manual_seed(100 + i)
+        w = (torch.randn(k, n, generator=gen, device=device, dtype=torch.float32) * 0.02).to(torch.float16)
+        full_layers.append(hidet_b200.symmetric_quantize(w, 'int8', dims=0))
+        del w
+    for m in MS_70B:
+        out_full = torch.empty(m, n, dtype=torch.float16, device=device)
+
+        def full_pass():
+            for wq_full, scale_full in full_layers:
+                hidet_b200.symmetric_quant_matmul(acts[m], wq_full, scale_full, out=out_full)
+
+        full_pass()
+        g_full = None
+        if graphs:
+            torch.cuda.current_stream().synchronize()
+            g_full = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g_full, stream=torch.cuda.current_stream()):
+                for _ in range(4):
+                    full_pass()
+        us_full = timed((lambda: g_full.replay()) if g_full is not None else (lambda: [full_pass() for _ in range(4)]), 5) * 1e3 / (4 * len(full_layers))
+        one_gpu.append(round(us_full, 2))
+        del g_full
+    for entry, us_full in zip(shapes, one_gpu):
+        entry['us_per_layer_one_gpu'] = us_full
+        entry['speedup_vs_one_gpu'] = round(us_full / entry['us_per_layer'], 2)
+    del full_layers
+
     # end to end: activations from pinned host memory in, gathered output back to the host, every step
     pinned_in = {m: acts[m].cpu().pin_memory() for m in MS_70B}
     pinned_out = {m: torch.empty(m, n, dtype=torch.float16).pin_memory() for m in MS_70B}
@@ -179,7 +216,28 @@ def run_sharded(args) -> int:
             'e2e': {'value': e2e_value, 'unit': 'GB/s', 'h2d_bytes_per_step': sum(t.numel() * 2 for t in pinned_in.values()),
                     'd2h_bytes_per_step': sum(t.numel() * 2 for t in pinned_out.values()), 'ms_per_step': e2e_ms},
         }
-        print(json.dumps(line))
+        line['speedup_vs_one_gpu'] = round(sum(one_gpu) / sum(e['us_per_layer'] for e in shapes), 2)
+        print(json.dumps(line), flush=True)
+    # Captured collectives keep the communicator alive: release the graphs before the process group.
+    graphs.clear()
+    torch.cuda.synchronize()
     dist.barrier()
+    _exit_if_teardown_stalls(30.0)
     dist.destroy_process_group()
     return 0
+
+
+def _exit_if_teardown_stalls(seconds: float) -> None:
+    """The result is printed and every rank has passed the last barrier; a communicator teardown that does not
+    finish in `seconds` must not keep the GPUs."""
+    import sys
+    import threading
+
+    def watchdog():
+        time.sleep(seconds)
+        sys.stdout.flush()
+        sys.stderr.write('bench: process group teardown still running after {:.0f} s, exiting\n'.format(seconds))
+        sys.stderr.flush()
+        os._exit(0)
+
+    threading.Thread(target=watchdog, daemon=True).start()

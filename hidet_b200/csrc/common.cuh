@@ -126,8 +126,14 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, uint32_
     return false;
 }
 
+// status[0] collects every wait that ran out (codes or-ed together: one failure starves the other
+// roles, whose waits then run out too); status[1] keeps the first one.
 __device__ __forceinline__ void report_timeout(unsigned int *status, unsigned int kernel, unsigned int site) {
-    if (status != nullptr) atomicOr(status, 0x80000000u | (site << 8) | kernel);
+    if (status != nullptr) {
+        const unsigned int code = 0x80000000u | (site << 8) | kernel;
+        atomicOr(status, code);
+        atomicCAS(status + 1, 0u, code);
+    }
 }
 
 // ---- TMA ----

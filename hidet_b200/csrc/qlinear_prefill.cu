@@ -53,6 +53,9 @@ struct Config {
     // of one stage overlaps that of the next ones (the ring must hold the stages being converted plus two).
     static constexpr int CONV_GROUPS = TM == 256 ? 2 : 4;
     static constexpr int GROUP_WARPS = CONV_WARPS / CONV_GROUPS;
+    // Stages after which the same converter group meets the same int8 slot again: lcm(RAW_SLOTS, CONV_GROUPS).
+    static constexpr int RAW_PERIOD = TM == 256 ? 6 : 4;
+    static_assert(RAW_PERIOD % RAW_SLOTS == 0 && RAW_PERIOD % CONV_GROUPS == 0, "RAW_PERIOD must be a common multiple");
     static constexpr int CONV_ROWS = GROUP_WARPS * 4;        // k-rows a group covers per pass (8 threads per row)
     static constexpr int MAIN_BYTES = ACT_BYTES + WF_BYTES;
     static constexpr int SMEM_BYTES = STAGES * MAIN_BYTES + RAW_SLOTS * RAW_BYTES + STAGING_BYTES + 1024;  // + alignment slack
@@ -145,8 +148,12 @@ __global__ void __launch_bounds__(THREADS, 1) qlinear_prefill_kn_kernel(const __
     using Cfg = Config<TM>;
     constexpr int STAGES = Cfg::STAGES, RAW_SLOTS = Cfg::RAW_SLOTS;
     constexpr int CONV_GROUPS = Cfg::CONV_GROUPS, GROUP_WARPS = Cfg::GROUP_WARPS, CONV_ROWS = Cfg::CONV_ROWS;
+    constexpr int RAW_PERIOD = Cfg::RAW_PERIOD;
     extern __shared__ unsigned char smem_dyn[];
-    __shared__ __align__(8) uint64_t raw_full[RAW_SLOTS];   // an int8 tile has landed
+    // An int8 tile has landed.  A parity wait tells a phase only from its neighbours, so a waiter has to
+    // see every phase of its barrier; successive uses of a slot can belong to different converter groups,
+    // hence one barrier per slot and group: the pair (slot, group) recurs every RAW_PERIOD stages.
+    __shared__ __align__(8) uint64_t raw_full[RAW_SLOTS][CONV_GROUPS];
     __shared__ __align__(8) uint64_t raw_empty[RAW_SLOTS];  // the converter group of that stage has read it
     __shared__ __align__(8) uint64_t act_full[STAGES];      // an activation tile has landed
     __shared__ __align__(8) uint64_t conv_full[STAGES];     // the converter group of that stage has written the f16 tile
@@ -170,7 +177,7 @@ __global__ void __launch_bounds__(THREADS, 1) qlinear_prefill_kn_kernel(const __
 
     if (threadIdx.x == 0) {
         for (int r = 0; r < RAW_SLOTS; ++r) {
-            mbar_init(smem_u32(&raw_full[r]), 1);
+            for (int g = 0; g < CONV_GROUPS; ++g) mbar_init(smem_u32(&raw_full[r][g]), 1);
             mbar_init(smem_u32(&raw_empty[r]), GROUP_WARPS);
         }
         for (int s = 0; s < STAGES; ++s) {
@@ -212,8 +219,9 @@ __global__ void __launch_bounds__(THREADS, 1) qlinear_prefill_kn_kernel(const __
                         ok = false;
                         break;
                     }
-                    mbar_expect_tx(smem_u32(&raw_full[r]), RAW_BYTES);
-                    tma_load_2d_hint(raw_addr(r), &map_w, n0, kb * BK, smem_u32(&raw_full[r]), keep);
+                    const uint32_t raw_bar = smem_u32(&raw_full[r][i % CONV_GROUPS]);  // the group that converts stage i
+                    mbar_expect_tx(raw_bar, RAW_BYTES);
+                    tma_load_2d_hint(raw_addr(r), &map_w, n0, kb * BK, raw_bar, keep);
                     const int s = i % STAGES;
                     const uint32_t use = i / STAGES;
                     if (use >= 1 && !mbar_wait(smem_u32(&slot_free[s]), (use - 1) & 1)) {
@@ -282,8 +290,9 @@ __global__ void __launch_bounds__(THREADS, 1) qlinear_prefill_kn_kernel(const __
                 const uint32_t use_r = i / RAW_SLOTS;
                 const int s = i % STAGES;
                 const uint32_t use = i / STAGES;
-                // the int8 tile must have landed, and the MMAs that read the f16 slot last time must be done
-                if (!mbar_wait(smem_u32(&raw_full[r]), use_r & 1) ||
+                // The int8 tile must have landed (on the barrier of this slot that belongs to this group),
+                // and the MMAs that read the f16 slot last time must be done.
+                if (!mbar_wait(smem_u32(&raw_full[r][group]), (i / RAW_PERIOD) & 1) ||
                     (use >= 1 && !mbar_wait(smem_u32(&slot_free[s]), (use - 1) & 1))) {
                     report_timeout(p.status, kKernelPrefill, 4);
                     ok = false;

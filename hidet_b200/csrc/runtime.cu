@@ -24,8 +24,9 @@ struct DeviceState {
 };
 DeviceState g_devices[kMaxDevices];
 
-// One status word per device, part of the loaded module image (no allocation at run time).
-__device__ unsigned int g_status_word = 0;
+// Two status words per device, part of the loaded module image (no allocation at run time): every
+// wait that ran out, or-ed together, and the first one.
+__device__ unsigned int g_status_word[2] = {0, 0};
 
 DeviceState *current_device_state() {
     int dev = -1;
@@ -119,13 +120,14 @@ B200Q_API int b200q_check_status(void) {
     unsigned int *word = b200q::device_status_word();
     if (word == nullptr) return b200q::set_error(B200Q_CUDA_ERROR, "no usable CUDA device for the calling thread");
     B200Q_CUDA_TRY(cudaDeviceSynchronize());
-    unsigned int v = 0;
-    B200Q_CUDA_TRY(cudaMemcpy(&v, word, sizeof(v), cudaMemcpyDeviceToHost));
-    if (v == 0) return B200Q_OK;
-    unsigned int zero = 0;
-    B200Q_CUDA_TRY(cudaMemcpy(word, &zero, sizeof(zero), cudaMemcpyHostToDevice));
-    return b200q::set_error(B200Q_KERNEL_TIMEOUT, "a bounded device-side wait ran out: kernel id %u, wait site %u (status 0x%08x)",
-                            v & 0xffu, (v >> 8) & 0xffu, v);
+    unsigned int v[2] = {0, 0};
+    B200Q_CUDA_TRY(cudaMemcpy(v, word, sizeof(v), cudaMemcpyDeviceToHost));
+    if (v[0] == 0) return B200Q_OK;
+    const unsigned int zero[2] = {0, 0};
+    B200Q_CUDA_TRY(cudaMemcpy(word, zero, sizeof(zero), cudaMemcpyHostToDevice));
+    return b200q::set_error(B200Q_KERNEL_TIMEOUT,
+                            "a bounded device-side wait ran out: first in kernel id %u at wait site %u; all that ran out, or-ed: 0x%08x",
+                            v[1] & 0xffu, (v[1] >> 8) & 0xffu, v[0]);
 }
 
 }  // extern "C"
