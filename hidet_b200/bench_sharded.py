@@ -106,6 +106,7 @@ def run_sharded(args) -> int:
                     with torch.cuda.graph(g, stream=side):
                         step(key)
                     graphs[key] = g
+                    del g
             timing = 'one CUDA graph per sweep'
         except Exception as e:  # capture is an optimisation of the measurement, not part of the product
             graphs = {}
@@ -219,10 +220,13 @@ def run_sharded(args) -> int:
         line['speedup_vs_one_gpu'] = round(sum(one_gpu) / sum(e['us_per_layer'] for e in shapes), 2)
         print(json.dumps(line), flush=True)
     # Captured collectives keep the communicator alive: release the graphs before the process group.
+    import gc
+
     graphs.clear()
+    gc.collect()
     torch.cuda.synchronize()
     dist.barrier()
-    _exit_if_teardown_stalls(30.0)
+    _exit_if_teardown_stalls(10.0)
     dist.destroy_process_group()
     return 0
 
