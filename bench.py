@@ -487,7 +487,7 @@ def main(argv=None) -> int:
     ap.add_argument('--no-cpu-baseline', action='store_true', help='skip the CPU leg (for profiling runs)')
     ap.add_argument('--no-extras', action='store_true', help='skip the prefill and quantize sections (for profiling runs)')
     ap.add_argument('--gather', choices=['nccl', 'p2p'], default=None,
-                    help='multi-GPU: how output slices reach every rank (default: p2p on two GPUs, nccl on more)')
+                    help='multi-GPU: how output slices reach every rank (default: p2p up to four GPUs, nccl on eight)')
     ap.add_argument('--m-list', default=None, help='multi-GPU: comma-separated activation row counts to sweep instead of 1,16,256,2048')
     ap.add_argument('--case', default=None, help='M,K,N: time one shape only (small case for profiling and tuning)')
     ap.add_argument('--layout', choices=['KN', 'NK'], default='KN', help='weight layout for --case')

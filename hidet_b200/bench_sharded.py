@@ -44,10 +44,11 @@ def run_sharded(args) -> int:
     if getattr(args, 'm_list', None):
         MS_70B = tuple(int(x) for x in args.m_list.split(','))
     if args.gather is None:
-        # Peer stores and peer copies are the faster delivery and the default on two GPUs.  On four and
-        # eight GPUs runs of that path ended in a launch failure whose cause is not known, so there the
-        # default is the NCCL all-gather.
-        args.gather = 'p2p' if world <= 2 else 'nccl'
+        # Peer stores and peer copies are the faster delivery and the default up to four GPUs, where they
+        # have been measured.  On eight GPUs the last run of that path ended in a launch failure, before a
+        # fault in the large-M kernel's barriers was found and fixed; it has not been run there since, so
+        # eight GPUs default to the NCCL all-gather, which has.
+        args.gather = 'p2p' if world <= 4 else 'nccl'
     begin, end = column_range(n, rank, world)
     n_local = end - begin
     copies = max(2, -(-(2 * 128 * 1024 * 1024) // (k * n_local)))
@@ -142,10 +143,12 @@ def run_sharded(args) -> int:
         us = ms_m * 1e3 / copies
         shapes.append({'M': m, 'K': k, 'N': n, 'us_per_layer': round(us, 2), 'GBps': round(algorithmic_bytes(m, k, n) / us / 1e3, 1),
                        'TFLOPS': round(2.0 * m * k * n / us / 1e6, 2)})
-        # the same without the gather: what the collective costs
+        # the same without the gather: what the delivery costs
+        c_local = torch.empty(m, n_local, dtype=torch.float16, device=device)
+
         def local_only():
             for layer in layers:
-                layer.local(acts[m])
+                layer.local(acts[m], out=c_local)
         us_local = timed(local_only, 5) * 1e3 / copies
         shapes[-1]['us_local_kernel'] = round(us_local, 2)
 
