@@ -38,6 +38,22 @@ K_DECODE = 4096
 DECODE_NS = (4096, 11008)
 DECODE_MS = (1, 4, 16)
 STACK = {4096: 16, 11008: 6}  # distinct weight matrices per width: 268 MB + 270 MB of int8
+# dram__bytes_read.sum + dram__bytes_write.sum of one launch of the small-M kernel, from an ncu capture of
+# `bench.py --case M,4096,N --launches 8 --eager` (summary: profiles/qlinear_decode_kn_kernel.md); keyed (M, N).
+# The output stays in L2, so the write counter reads 0 to 9 KB.
+NCU_DRAM_BYTES = {(1, 4096): 16825088, (16, 4096): 16951552, (1, 11008): 45155072, (16, 11008): 45285632}
+
+
+def ncu_traffic_per_launch() -> float:
+    """Average DRAM traffic per launch over the launch mix of one step; M = 4 was not captured and is taken
+    on the line between M = 1 and M = 16."""
+    total, launches = 0.0, 0
+    for n, count in STACK.items():
+        lo, hi = NCU_DRAM_BYTES[(1, n)], NCU_DRAM_BYTES[(16, n)]
+        for m in DECODE_MS:
+            total += count * (lo + (hi - lo) * (m - 1) / 15.0)
+            launches += count
+    return total / launches
 
 K_70B, N_70B = 8192, 28672
 MS_70B = (1, 16, 256, 2048)
@@ -409,7 +425,9 @@ def run_single_gpu(args) -> int:
         'gpu_launches': launches_per_step * args.steps,
         'clocks': clocks.summary(),
         'roofline': {'bound': 'hbm', 'achieved': value, 'peak': peaks['hbm_gbs'], 'unit': 'GB/s', 'frac': value / peaks['hbm_gbs'],
-                     'traffic': None, 'peak_source': peaks['source'] + ' (burst copy)', 'kernel': 'qlinear_decode_kn_kernel'},
+                     'traffic': ncu_traffic_per_launch(), 'traffic_unit': 'bytes per launch (ncu, average over the step\'s launch mix)',
+                     'algorithmic_bytes_per_launch': bytes_per_step / launches_per_step,
+                     'peak_source': peaks['source'] + ' (burst copy)', 'kernel': 'qlinear_decode_kn_kernel'},
         'shapes': shapes,
         'e2e': {'value': e2e_value, 'unit': 'GB/s', 'h2d_bytes_per_step': h2d, 'd2h_bytes_per_step': d2h, 'ms_per_step': e2e_ms,
                 'note': 'hidet_b200.CudaGraph.run_async per M (pinned host activations copied in, 22 quantized linears replayed), result copied back to pinned host memory, one synchronisation per step'},
