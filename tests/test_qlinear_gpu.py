@@ -233,3 +233,21 @@ def test_qlinear_into_a_column_range_of_wider_outputs(m, k, n):
         with pytest.raises(ffi.BackendException, match='one destination'):
             _to_destinations(a, wq_t, scale_t, dsts + dsts, ldc, col0)
     assert ffi.func('b200q_check_status')() == ffi.OK
+
+
+def test_push_columns_copies_one_column_range_and_nothing_else():
+    import ctypes
+
+    rows, ld, col0, cols = 37, 512, 96, 200
+    src = torch.randn(rows, ld, device='cuda').half()
+    dsts = [torch.full((rows, ld), -3.0, dtype=torch.float16, device='cuda') for _ in range(2)]
+    table = (ctypes.c_void_p * 3)(src.data_ptr(), dsts[0].data_ptr(), dsts[1].data_ptr())  # the first entry is the source itself
+    before = src.clone()
+    ffi.func('b200q_push_columns')(src.data_ptr(), table, 3, rows, cols, ld, col0, torch.cuda.current_stream().cuda_stream)
+    torch.cuda.synchronize()
+    assert torch.equal(src, before)
+    for d in dsts:
+        assert torch.equal(d[:, col0:col0 + cols], src[:, col0:col0 + cols])
+        assert bool((d[:, :col0] == -3.0).all()) and bool((d[:, col0 + cols:] == -3.0).all())
+    with pytest.raises(ffi.BackendException, match='do not fit'):
+        ffi.func('b200q_push_columns')(src.data_ptr(), table, 3, rows, cols, ld, ld - cols + 1, torch.cuda.current_stream().cuda_stream)
