@@ -1,6 +1,6 @@
 """Generates tests/golden/reference_cpu_*.npz by running the reference (hidet-org/hidet) itself.
 
-Needs the reference checkout (default /root/reference, override with HIDET_REFERENCE) and cmake, g++.
+Needs the reference checkout (its path in the environment variable HIDET_REFERENCE) and cmake, g++.
 It only runs where the checkout exists; the fixtures it writes are committed so that the tests need
 neither.  Nothing is written into the checkout: its runtime library is built out of tree, and its
 python package is imported from a scratch copy (the package looks for its native libraries relative
@@ -25,7 +25,7 @@ import textwrap
 import numpy as np
 
 HERE = os.path.dirname(os.path.abspath(__file__))
-REFERENCE = os.environ.get('HIDET_REFERENCE', '/root/reference')
+REFERENCE = os.environ.get('HIDET_REFERENCE', '')
 
 
 def prepare_reference(scratch: str) -> None:
@@ -104,6 +104,9 @@ def main() -> int:
     ap = argparse.ArgumentParser()
     ap.add_argument('--scratch', default='/tmp/hidet_reference_scratch')
     args = ap.parse_args()
+    if not os.path.isdir(os.path.join(REFERENCE, 'python', 'hidet')):
+        print('set HIDET_REFERENCE to a checkout of hidet-org/hidet', file=sys.stderr)
+        return 2
     prepare_reference(args.scratch)
     hidet = import_reference(args.scratch)
     import torch

@@ -1,0 +1,50 @@
+"""The large-M kernel's barrier protocol, model-checked on the host under random schedules (no GPU)."""
+import dataclasses
+import random
+
+import pytest
+
+from pipeline_model import Pipeline, PipelineConfig, ProtocolError, config_from_source
+
+
+@pytest.mark.parametrize('tm', [256, 64])
+def test_kernel_configuration_is_consistent(tm):
+    cfg = config_from_source(tm)
+    assert cfg.group_warps * cfg.conv_groups == 8
+    # the (slot, group) pair of stage i is (i % raw_slots, i % conv_groups): it recurs with the least common multiple
+    lcm = next(n for n in range(1, 1000) if n % cfg.raw_slots == 0 and n % cfg.conv_groups == 0)
+    assert cfg.raw_period == lcm
+    # a group converting a stage needs its int8 slot and its f16 slot at once, and the ring must hold the
+    # stages under conversion plus the ones the tensor core works on
+    assert cfg.stages >= cfg.conv_groups + 2 or cfg.stages >= 4
+    assert cfg.raw_slots >= cfg.conv_groups or cfg.raw_slots >= 3
+
+
+@pytest.mark.parametrize('tm', [256, 64])
+@pytest.mark.parametrize('tiles,k_blocks', [(1, 1), (1, 7), (3, 8), (5, 13), (2, 64)])
+def test_protocol_holds_under_random_schedules(tm, tiles, k_blocks):
+    cfg = config_from_source(tm)
+    for seed in range(40):
+        for delay in (0.2, 0.9, 0.99):   # copies land promptly ... copies land very late and far out of order
+            Pipeline(cfg, tiles, k_blocks, random.Random(seed)).run(copy_delay=delay)
+
+
+def test_model_catches_a_shared_barrier_for_slots_that_change_groups():
+    """Three int8 slots taken in turn by two converter groups with ONE barrier per slot: a group that skipped a use
+    of a slot takes the pending phase of the other group's copy for its own.  The model must find that."""
+    cfg = dataclasses.replace(config_from_source(256), per_group_barriers=False)
+    assert cfg.raw_slots % cfg.conv_groups != 0
+    failures = 0
+    for seed in range(60):
+        try:
+            Pipeline(cfg, 3, 16, random.Random(seed)).run(copy_delay=0.9)
+        except ProtocolError:
+            failures += 1
+    assert failures > 0
+
+
+def test_shared_barrier_is_fine_when_every_slot_keeps_its_group():
+    cfg = dataclasses.replace(config_from_source(64), per_group_barriers=False)
+    assert cfg.raw_slots % cfg.conv_groups == 0
+    for seed in range(30):
+        Pipeline(cfg, 3, 16, random.Random(seed)).run(copy_delay=0.9)
