@@ -211,7 +211,7 @@ def run_sharded(args) -> int:
                        'weights_in_rotation': copies, 'l2': 'inputs larger than L2: {} distinct weight shards of {} MB per rank'.format(copies, k * n_local // 1000000),
                        'timing': timing + ', CUDA events, barrier on both sides, max over ranks'},
             'tflops': flops_per_step / (ms_per_step * 1e-3) / 1e12,
-            'gpu_launches': len(MS_70B) * copies * args.steps,
+            'gpu_launches': sum(2 if (args.gather == 'p2p' and m >= ColumnParallelQuantLinear.SPLIT_ROWS_FROM) else 1 for m in MS_70B) * copies * args.steps,
             'clocks': clocks.summary(),
             'roofline': {'bound': 'hbm for M <= 16, tensor for M >= 256', 'achieved': value, 'peak': peaks['hbm_gbs'] * world, 'unit': 'GB/s',
                          'frac': value / (peaks['hbm_gbs'] * world), 'traffic': None, 'peak_source': peaks['source'] + ' (burst copy) x n_gpus',
