@@ -174,7 +174,7 @@ class ColumnParallelQuantLinear:
         import ctypes
 
         from . import ffi
-        from .runtime import current_stream_ptr, workspaces
+        from .runtime import workspaces
 
         lead = tuple(x.shape[:-1])
         rows = 1

@@ -10,7 +10,6 @@ from __future__ import annotations
 
 from typing import Any, Dict, List, Optional
 
-import torch
 import torch.fx as fx
 
 from .transforms import PassContext, optimize

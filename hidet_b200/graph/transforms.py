@@ -12,11 +12,10 @@ placeholder bound to a parameter at compile time.
 """
 from __future__ import annotations
 
-from typing import Any, Callable, Dict, List, Optional, Type
+from typing import Any, Dict, List, Optional, Type
 
 import torch
 import torch.fx as fx
-import torch.nn.functional as F
 
 from .. import quant
 from ..quant.resolve import resolve_k_parts

@@ -1,5 +1,4 @@
 """Operator objects, the quantization pass over fx graphs and the torch.compile backend on the GPU."""
-import numpy as np
 import pytest
 import torch
 import torch.fx as fx

@@ -4,7 +4,7 @@ import random
 
 import pytest
 
-from pipeline_model import Pipeline, PipelineConfig, ProtocolError, config_from_source
+from pipeline_model import Pipeline, ProtocolError, config_from_source
 
 
 @pytest.mark.parametrize('tm', [256, 64])

@@ -10,7 +10,6 @@ caller-allocated workspace.  Both run the same deterministic kernel, so the outp
 The file name sorts last on purpose: a run that stops at the first failure has then already run every
 other test.
 """
-import numpy as np
 import pytest
 import torch
 
