@@ -9,16 +9,18 @@
 // is the MMA's 16-row operand and the activations its 8-column operand, so up to 8 activation rows
 // cost one MMA per 16 x 16 weight block and up to 16 rows two (rows beyond M are zero-filled by TMA).
 //
-// K is split across CTAs to fill the machine.  Up to 16 splits of one output tile form a thread-block
-// cluster: every CTA stores its partial tile into the shared memory of the CTA that owns those
-// columns, one cluster barrier later the owner adds the partials in rank order, applies the per-column
-// scale and rounds to f16 once.  More splits than a cluster holds go through a caller-provided fp32
-// workspace, where the last CTA of a tile to arrive does the same.  Either way the order of every sum
-// is fixed, so results are the same on every run.
+// K is split across CTAs to fill the machine.  Up to 8 splits of one output tile form a thread-block
+// cluster: every CTA sends its partial tile into the shared memory of the CTA that owns those columns
+// with asynchronous remote stores that count bytes on an mbarrier of the owner (no cluster barrier
+// round trip); the owner waits for the byte count, adds the partials in rank order, applies the
+// per-column scale and rounds to f16 once.  More splits than a cluster holds go through a
+// caller-provided fp32 workspace, where the last CTA of a tile to arrive does the same.  Either way
+// the order of every sum is fixed, so results are the same on every run.
 //
 // The kernel is launched as a programmatic dependent of the kernel before it in the stream: weight
-// tiles do not depend on that kernel, so they are requested before waiting for it, and the kernel after
-// this one is allowed to start once the main loop is over.
+// tiles and scales do not depend on that kernel, so they are requested before waiting for it, and the
+// kernel after this one is allowed to start once the main loop is over.  (Letting it start earlier was
+// measured and is slower: its weight requests then queue in front of this kernel's own.)
 //
 // Replaces the generated mma.sync kernel of python/hidet/graph/ops/quant/matmul_f16_i8.py:136-485
 // (f16 accumulation, 64x128 tiles, no split-K by default) for M <= 16, and serves larger M by
@@ -38,11 +40,14 @@ constexpr int THREADS = 32 * (CONSUMER_WARPS + 1);
 constexpr int W_STAGE_BYTES = BK * BN;       // 8192
 constexpr int A_STAGE_BYTES = BM * BK * 2;   // 2048
 constexpr int PIPE_BYTES = STAGES * (W_STAGE_BYTES + A_STAGE_BYTES);
-constexpr int RECV_BYTES = BM * (BN + 8) * 4; // partial tiles pushed by the CTAs of the cluster: [rank][row][ceil(BN / ranks)] fp32
+constexpr int RECV_COLS = 168;               // most columns the slices of a cluster cover together (7 ranks x 24 columns)
+constexpr int RECV_BYTES = BM * RECV_COLS * 4; // partial tiles sent by the CTAs of the cluster: [rank][row][cols_per] fp32
+constexpr int STAGING_ROW = 36;              // floats per row of a warp's 32-column staging block (padded: conflict-free)
 constexpr int SMEM_BYTES = PIPE_BYTES + RECV_BYTES + 1024;  // + alignment slack
+static_assert(CONSUMER_WARPS * BM * STAGING_ROW * 4 <= STAGES * W_STAGE_BYTES, "the staging blocks reuse the weight ring");
 constexpr int kCtasPerSm = 4;                // resident CTAs per SM the plan aims at
 constexpr int64_t kMaxCounters = 65536;      // arrival counters at the head of the workspace
-constexpr int kMaxCluster = 8;               // largest cluster a B200 schedules (8 is the portable limit)
+constexpr int kMaxCluster = 8;               // largest cluster of the plan (8 is the portable limit; the reduction reads up to eight partials)
 
 __device__ __forceinline__ uint2 lds64(uint32_t addr) {
     uint2 v;
@@ -93,7 +98,6 @@ __device__ __forceinline__ uint32_t cluster_nctarank() {
     asm volatile("mov.u32 %0, %%cluster_nctarank;" : "=r"(r));
     return r;
 }
-__device__ __forceinline__ void cluster_arrive_relaxed() { asm volatile("barrier.cluster.arrive.relaxed.aligned;" ::: "memory"); }
 __device__ __forceinline__ void cluster_arrive_release() { asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory"); }
 __device__ __forceinline__ void cluster_wait_acquire() { asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory"); }
 // Address of the same shared-memory location in CTA `rank` of the cluster.
@@ -102,9 +106,39 @@ __device__ __forceinline__ uint32_t map_to_rank(uint32_t local_addr, uint32_t ra
     asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(local_addr), "r"(rank));
     return r;
 }
-__device__ __forceinline__ void st_cluster_f32(uint32_t addr, float v) {
-    asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(addr), "f"(v) : "memory");
+// Asynchronous stores into the shared memory of a CTA of the cluster; each adds its size to the transaction
+// count of an mbarrier of that CTA once the data is there.
+__device__ __forceinline__ void st_async_f32(uint32_t addr, float v, uint32_t bar) {
+    asm volatile("st.async.weak.shared::cluster.mbarrier::complete_tx::bytes.b32 [%0], %1, [%2];" ::"r"(addr), "r"(__float_as_uint(v)), "r"(bar) : "memory");
 }
+__device__ __forceinline__ void st_async_v4f32(uint32_t addr, float4 v, uint32_t bar) {
+    asm volatile("st.async.weak.shared::cluster.mbarrier::complete_tx::bytes.v4.b32 [%0], {%1, %2, %3, %4}, [%5];" ::"r"(addr),
+                 "r"(__float_as_uint(v.x)), "r"(__float_as_uint(v.y)), "r"(__float_as_uint(v.z)), "r"(__float_as_uint(v.w)), "r"(bar)
+                 : "memory");
+}
+// Bounded wait on an mbarrier phase that remote CTAs complete (acquire at cluster scope).
+__device__ __forceinline__ bool mbar_wait_cluster(uint32_t bar, uint32_t parity) {
+    for (uint32_t i = 0; i < kSpinLimit; ++i) {
+        uint32_t ok;
+        asm volatile(
+            "{\n\t"
+            ".reg .pred p;\n\t"
+            "mbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2, %3;\n\t"
+            "selp.u32 %0, 1, 0, p;\n\t"
+            "}\n"
+            : "=r"(ok)
+            : "r"(bar), "r"(parity), "r"(kWaitHintNs)
+            : "memory");
+        if (ok) return true;
+    }
+    return false;
+}
+__device__ __forceinline__ float4 lds128f(uint32_t addr) {
+    float4 v;
+    asm volatile("ld.shared.v4.f32 {%0, %1, %2, %3}, [%4];" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "r"(addr));
+    return v;
+}
+__device__ __forceinline__ void sts32f(uint32_t addr, float v) { asm volatile("st.shared.f32 [%0], %1;" ::"r"(addr), "f"(v) : "memory"); }
 
 constexpr int kModeDirect = 0;  // one CTA per output tile
 constexpr int kModeSplit = 1;   // `splits` CTAs per tile: clusters of `cluster` CTAs, `groups` clusters per tile
@@ -126,6 +160,7 @@ struct Params {
     int k_begin, k_end;       // the k range this launch sums over (k_end is also the tensor maps' K extent)
     int iters_per_split;      // BK-sized k steps per split
     int groups;               // clusters per output tile (splits = groups * cluster size)
+    int cols_per;             // columns of a tile each CTA of the cluster owns in the reduction (a multiple of 8)
     int mode;                 // kModeDirect or kModeSplit
 };
 
@@ -137,6 +172,7 @@ __global__ void __launch_bounds__(THREADS) qlinear_decode_kn_kernel(const __grid
     extern __shared__ unsigned char smem_dyn[];
     __shared__ __align__(8) uint64_t full_bar[STAGES];
     __shared__ __align__(8) uint64_t empty_bar[STAGES];
+    __shared__ __align__(8) uint64_t recv_bar;  // the partial tiles of this CTA's columns have landed
     __shared__ unsigned int is_last;
 
     // 128B-swizzled TMA tiles need 1024-byte aligned bases.
@@ -159,18 +195,39 @@ __global__ void __launch_bounds__(THREADS) qlinear_decode_kn_kernel(const __grid
     int n_iters = total_iters - it_begin;
     if (n_iters > p.iters_per_split) n_iters = p.iters_per_split;
     if (n_iters < 0) n_iters = 0;
+    int rows = p.M - m0;
+    if (rows > BM) rows = BM;
+    const uint32_t nranks = cluster_nctarank();
+    const uint32_t rank = cluster_ctarank();
+    const int cols_per = p.cols_per;
+    // Columns of the tile this CTA sums in the reduction: [own_first, own_first + own_cols).
+    const int own_first = (int)rank * cols_per;
+    int own_cols = BN - own_first;
+    if (own_cols > cols_per) own_cols = cols_per;
+    if (own_cols < 0) own_cols = 0;
     if (threadIdx.x == 0) {
 #pragma unroll
         for (int s = 0; s < STAGES; ++s) {
             mbar_init(smem_u32(&full_bar[s]), 2);  // one arrival for the weight tile, one for the activation tile
             mbar_init(smem_u32(&empty_bar[s]), CONSUMER_WARPS);
         }
+        mbar_init(smem_u32(&recv_bar), 1);
         mbar_fence_init();
+        // Bytes the cluster will send here: every rank, `rows` rows of this CTA's columns.
+        if (p.mode == kModeSplit && own_cols > 0) mbar_expect_tx(smem_u32(&recv_bar), nranks * (uint32_t)rows * (uint32_t)own_cols * 4u);
     }
     __syncthreads();
     // First half of a cluster barrier whose second half sits in front of the first remote store: by
-    // then every CTA of the cluster has started, which remote shared-memory access requires.
-    cluster_arrive_relaxed();
+    // then every CTA of the cluster has started and set up its barriers, which remote access requires.
+    cluster_arrive_release();
+
+    // The result element this thread finishes in the split-K reduction, and its scale.  Like the weight, the
+    // scale does not depend on the kernel before this one, so it is fetched now, far from where it is used.
+    float sc_own = 0.0f;
+    if (p.mode == kModeSplit) {
+        const int cc = (int)threadIdx.x % cols_per;
+        if (cc < own_cols && n0 + own_first + cc < p.N) sc_own = __half2float(__ldg(p.scale + n0 + own_first + cc));
+    }
 
     // acc[j][mt][.]: 16 x 8 tile j of this warp's 32 columns, activation rows 8 * mt ... 8 * mt + 7.
     // Element (column 16 j + 8 h + g, row 8 mt + 2t + e) is acc[j][mt][2h + e].
@@ -260,10 +317,9 @@ __global__ void __launch_bounds__(THREADS) qlinear_decode_kn_kernel(const __grid
             }
         }
     }
+    __syncwarp();  // the role branches above are lane-divergent; the cluster barrier below wants whole warps
     pdl_launch_dependents();  // the next kernel may start streaming its weight
 
-    int rows = p.M - m0;
-    if (rows > BM) rows = BM;
     const bool consumer = warp < CONSUMER_WARPS;
     // This thread's four columns inside the tile: 32 warp + 16 j + 8 h + g.
     const int col_base = 32 * warp + g;
@@ -292,43 +348,79 @@ __global__ void __launch_bounds__(THREADS) qlinear_decode_kn_kernel(const __grid
     }
 
     // ---------------- split-K ----------------
-    // Level 1, inside a cluster: every CTA stores its partial tile into the shared memory of the CTA
-    // that owns those columns; one cluster barrier later the owner holds the partials of all ranks.
-    // (Without a cluster the CTA is its own owner and the same code runs on local shared memory.)
-    const uint32_t nranks = cluster_nctarank();
-    const uint32_t rank = cluster_ctarank();
-    const int cols_per = (BN + (int)nranks - 1) / (int)nranks;  // columns per owner (the last owner may have fewer)
-    cluster_wait_acquire();                 // every CTA of the cluster is running
+    // Level 1, inside a cluster: every CTA sends its partial tile into the shared memory of the CTA that
+    // owns those columns, counted in bytes on the owner's barrier; the owner then holds the partials of all
+    // ranks.  (Without a cluster the CTA is its own owner and the same code runs on local shared memory.)
+    // recv layout: [rank][row][cols_per] fp32.
+    cluster_wait_acquire();  // every CTA of the cluster is running
     if (consumer) {
+        if (rows <= 2) {
+            // One or two rows live in the lanes with t == 0: a few scalar remote stores, no staging.
+            if (t == 0) {
 #pragma unroll
-        for (int j = 0; j < 2; ++j)
+                for (int j = 0; j < 2; ++j)
 #pragma unroll
-            for (int h = 0; h < 2; ++h) {
-                const int col = col_base + 16 * j + 8 * h;
-                const uint32_t owner = (uint32_t)(col / cols_per);
-                const int col_in = col - (int)owner * cols_per;
-                const uint32_t remote = map_to_rank(recv_base, owner);
+                    for (int h = 0; h < 2; ++h) {
+                        const int col = col_base + 16 * j + 8 * h;
+                        const uint32_t owner = (uint32_t)(col / cols_per);
+                        const int col_in = col - (int)owner * cols_per;
+                        const uint32_t remote = map_to_rank(recv_base, owner);
+                        const uint32_t rbar = map_to_rank(smem_u32(&recv_bar), owner);
 #pragma unroll
-                for (int mt = 0; mt < MT; ++mt)
-#pragma unroll
-                    for (int e = 0; e < 2; ++e) {
-                        const int r = 8 * mt + 2 * t + e;
-                        if (r < rows) st_cluster_f32(remote + (((int)rank * BM + r) * cols_per + col_in) * 4, acc[j][mt][2 * h + e]);
+                        for (int e = 0; e < 2; ++e)
+                            if (e < rows) st_async_f32(remote + (((int)rank * BM + e) * cols_per + col_in) * 4, acc[j][0][2 * h + e], rbar);
                     }
             }
+        } else {
+            // More rows: transpose through a staging block in the (now idle) weight ring, then 16-byte remote stores.
+            asm volatile("bar.sync 1, %0;" ::"n"(32 * CONSUMER_WARPS) : "memory");  // every consumer warp is done with the ring
+            const uint32_t stage_w = w_base + warp * (BM * STAGING_ROW * 4);
+#pragma unroll
+            for (int j = 0; j < 2; ++j)
+#pragma unroll
+                for (int h = 0; h < 2; ++h)
+#pragma unroll
+                    for (int mt = 0; mt < MT; ++mt)
+#pragma unroll
+                        for (int e = 0; e < 2; ++e) sts32f(stage_w + ((8 * mt + 2 * t + e) * STAGING_ROW + 16 * j + 8 * h + g) * 4, acc[j][mt][2 * h + e]);
+            __syncwarp();
+            // lane -> row lane / 8 of each pass of four rows, columns 4 (lane % 8) .. + 3
+            const int rr = lane >> 3, v4 = lane & 7;
+            const int col = 32 * warp + 4 * v4;
+            const uint32_t owner = (uint32_t)(col / cols_per);
+            const int col_in = col - (int)owner * cols_per;
+            const uint32_t remote = map_to_rank(recv_base, owner) + (((int)rank * BM) * cols_per + col_in) * 4;
+            const uint32_t rbar = map_to_rank(smem_u32(&recv_bar), owner);
+#pragma unroll
+            for (int pass = 0; pass < BM / 4; ++pass) {
+                const int r = pass * 4 + rr;
+                if (r < rows) st_async_v4f32(remote + r * cols_per * 4, lds128f(stage_w + (r * STAGING_ROW + 4 * v4) * 4), rbar);
+            }
+        }
     }
-    cluster_arrive_release();
-    cluster_wait_acquire();  // all partial tiles of this CTA's columns have landed
-    const int col_first = n0 + (int)rank * cols_per;  // first column this CTA owns
+    if (own_cols > 0) {
+        if (!mbar_wait_cluster(smem_u32(&recv_bar), 0)) report_timeout(p.status, kKernelDecode, 4);
+    }
+    // Owner: one result element per thread and round; element i is row i / cols_per, column i % cols_per of
+    // the slice.  The partials of the (at most eight) ranks are read together and added in rank order.
+    const int col_first = n0 + own_first;  // first column this CTA owns
+    auto sum_ranks = [&](int r, int cc) {
+        float v[8];
+#pragma unroll
+        for (int jr = 0; jr < 8; ++jr) v[jr] = jr < (int)nranks ? recv[(jr * BM + r) * cols_per + cc] : 0.0f;
+        float sum = v[0];
+#pragma unroll
+        for (int jr = 1; jr < 8; ++jr) sum += v[jr];
+        return sum;
+    };
     if (p.groups == 1) {
         for (int idx = threadIdx.x; idx < rows * cols_per; idx += THREADS) {
             const int r = idx / cols_per;
             const int cc = idx - r * cols_per;
             const int nn = col_first + cc;
-            if (nn < p.N && (int)rank * cols_per + cc < BN) {
-                float v = 0.0f;
-                for (uint32_t jr = 0; jr < nranks; ++jr) v += recv[((int)jr * BM + r) * cols_per + cc];
-                store_out(p.out, m0 + r, nn, __float2half_rn(v * __half2float(p.scale[nn])));
+            if (nn < p.N && cc < own_cols) {
+                const float sc = idx < THREADS ? sc_own : __half2float(p.scale[nn]);
+                store_out(p.out, m0 + r, nn, __float2half_rn(sum_ranks(r, cc) * sc));
             }
         }
         return;
@@ -342,11 +434,7 @@ __global__ void __launch_bounds__(THREADS) qlinear_decode_kn_kernel(const __grid
         const int r = idx / cols_per;
         const int cc = idx - r * cols_per;
         const int nn = col_first + cc;
-        if (nn < p.N && (int)rank * cols_per + cc < BN) {
-            float v = 0.0f;
-            for (uint32_t jr = 0; jr < nranks; ++jr) v += recv[((int)jr * BM + r) * cols_per + cc];
-            __stcg(&p.partial[((size_t)group * p.M + (m0 + r)) * p.N + nn], v);
-        }
+        if (nn < p.N && cc < own_cols) __stcg(&p.partial[((size_t)group * p.M + (m0 + r)) * p.N + nn], sum_ranks(r, cc));
     }
     __threadfence();
     __syncthreads();
@@ -362,11 +450,11 @@ __global__ void __launch_bounds__(THREADS) qlinear_decode_kn_kernel(const __grid
         const int r = idx / cols_per;
         const int cc = idx - r * cols_per;
         const int nn = col_first + cc;
-        if (nn < p.N && (int)rank * cols_per + cc < BN) {
+        if (nn < p.N && cc < own_cols) {
             float v = 0.0f;
 #pragma unroll 4
             for (int gr = 0; gr < p.groups; ++gr) v += __ldcg(&p.partial[((size_t)gr * p.M + (m0 + r)) * p.N + nn]);
-            store_out(p.out, m0 + r, nn, __float2half_rn(v * __half2float(p.scale[nn])));
+            store_out(p.out, m0 + r, nn, __float2half_rn(v * (idx < THREADS ? sc_own : __half2float(p.scale[nn]))));
         }
     }
     if (threadIdx.x == 0) p.counters[slot] = 0;  // leave the workspace ready for the next call
@@ -459,6 +547,7 @@ int launch_decode_kn(const void *a, const void *wq, const void *scale, void *c, 
     p.k_end = (int)k_end;
     p.iters_per_split = pl.iters_per_split;
     p.groups = pl.groups;
+    p.cols_per = (int)round_up(ceil_div(BN, pl.cluster), 8);
     p.mode = pl.splits == 1 ? kModeDirect : kModeSplit;
 
     auto kernel = (M - (int64_t)(pl.m_tiles - 1) * BM <= 8 && pl.m_tiles == 1) ? qlinear_decode_kn_kernel<1> : qlinear_decode_kn_kernel<2>;
