@@ -12,6 +12,7 @@ from .cuda_graph import CudaGraph
 from .quant import (
     symmetric_quantize,
     symmetric_dequantize,
+    symmetric_dequantize_take,
     symmetric_quant_matmul,
     symmetric_quant_matmul_f16_i8,
     symmetric_quant_matmul_atomic_f16_i8,

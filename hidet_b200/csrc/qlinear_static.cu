@@ -62,9 +62,13 @@ B200Q_API int b200q_qlinear_f16_i8_static(const void *a, const void *wq, const v
     if (w_layout != B200Q_LAYOUT_KN) return set_error(B200Q_UNSUPPORTED, "qlinear_f16_i8_static: only the [K, N] weight layout is served here");
     if (M > 2147483647LL || N > 2147483647LL || K > 2147483647LL) return set_error(B200Q_UNSUPPORTED, "qlinear_f16_i8_static: sizes beyond 2^31-1 are not supported");
     if (M == 0 || N == 0) return B200Q_OK;
-    if (a == nullptr || wq == nullptr || scale == nullptr || c == nullptr) return set_error(B200Q_INVALID_ARGUMENT, "qlinear_f16_i8_static: null pointer argument");
-    if (K == 0) return set_error(B200Q_INVALID_ARGUMENT, "qlinear_f16_i8_static: K must be positive");
+    if (scale == nullptr || c == nullptr) return set_error(B200Q_INVALID_ARGUMENT, "qlinear_f16_i8_static: null output or scale pointer");
     cudaStream_t s = static_cast<cudaStream_t>(stream);
+    if (K == 0) {  // an empty sum, as in b200q_qlinear_f16_i8
+        B200Q_CUDA_TRY(cudaMemsetAsync(c, 0, (size_t)M * N * sizeof(__half), s));
+        return B200Q_OK;
+    }
+    if (a == nullptr || wq == nullptr) return set_error(B200Q_INVALID_ARGUMENT, "qlinear_f16_i8_static: null input pointer");
     if (!decode_kn_supported(a, wq, N, K)) {
         return set_error(B200Q_UNSUPPORTED, "qlinear_f16_i8_static: operands need 16-byte aligned bases and rows (N %% 16 == 0, K %% 8 == 0); "
                                             "got N=%lld K=%lld", (long long)N, (long long)K);
@@ -84,8 +88,10 @@ B200Q_API int b200q_qlinear_f16_i8_static(const void *a, const void *wq, const v
         int rc = static_scratch(&scratch);
         if (rc != B200Q_OK) return rc;
         // The arrival counters must read zero when the kernel starts.  A completed call leaves them
-        // zero, but the array is shared by every caller and survives failed calls, so clear them here.
-        B200Q_CUDA_TRY(cudaMemsetAsync(scratch, 0, plan.counter_bytes, s));
+        // zero, but the array is shared by every caller and survives failed calls, so clear the ones
+        // this problem uses (one per output tile and cluster rank) here.
+        const size_t used = (size_t)plan.n_tiles * plan.m_tiles * plan.cluster * sizeof(unsigned int);
+        B200Q_CUDA_TRY(cudaMemsetAsync(scratch, 0, used < plan.counter_bytes ? used : plan.counter_bytes, s));
     }
     return launch_decode_kn(a, wq, scale, c, M, N, K, 0, K, true, scratch, need, s);
 }

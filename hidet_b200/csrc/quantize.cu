@@ -342,6 +342,40 @@ __global__ void __launch_bounds__(kThreads) dequantize_kernel(const Q *__restric
 
 bool aligned(const void *p, size_t a) { return (reinterpret_cast<uintptr_t>(p) % a) == 0; }
 
+// ---------------------------------------------------------------------------------------------
+// embedding lookup in a row-quantized table: out[i, :] = T(table[idx[i], :]) * scale[idx[i]]
+// ---------------------------------------------------------------------------------------------
+// One vector of VEC values per thread, `vec_per_row` threads' worth per looked-up row.  The arithmetic is
+// that of dequantize_kernel with reduce_dim = 1, so a lookup equals the row of the dequantized table bit
+// for bit.  An index outside [0, vocab) (after adding vocab to a negative one) yields a row of zeros and
+// sets bit 30 of the device status word.
+template <typename T, typename Q, typename I, int VEC>
+__global__ void __launch_bounds__(kThreads) embedding_dequant_kernel(const Q *__restrict__ table, const T *__restrict__ scale,
+                                                                     const I *__restrict__ idx, T *__restrict__ out, int64_t vocab,
+                                                                     int64_t dim, int64_t n_idx, unsigned int *status) {
+    using A = Arith<T>;
+    const int64_t vec_per_row = dim / VEC;
+    const int64_t total = n_idx * vec_per_row;
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
+        const int64_t r = i / vec_per_row;
+        const int64_t c = (i - r * vec_per_row) * VEC;
+        int64_t row = (int64_t)idx[r];
+        if (row < 0) row += vocab;
+        Vec<T, VEC> o;
+        if (row < 0 || row >= vocab) {
+#pragma unroll
+            for (int e = 0; e < VEC; ++e) o.v[e] = (T)0.0f;
+            if (c == 0 && status != nullptr) atomicOr(status, 0x40000000u);
+        } else {
+            const Vec<Q, VEC> q = load_vec<Q, VEC>(table + row * dim + c);
+            const T s = scale[row];
+#pragma unroll
+            for (int e = 0; e < VEC; ++e) o.v[e] = A::template dequant<Q>(q.v[e], s);
+        }
+        store_vec<T, VEC>(out + r * dim + c, o);
+    }
+}
+
 // Largest dynamic shared memory a quantize_cols CTA may ask for (the static arrays need a little).
 constexpr size_t kMaxTileBytes = 200 * 1024;
 
@@ -432,6 +466,30 @@ int dequantize_typed(const void *wq_, const void *scale_, void *w_, int64_t rows
     return B200Q_OK;
 }
 
+template <typename T, typename Q, typename I>
+int embedding_typed(const void *table_, const void *scale_, const void *idx_, void *out_, int64_t vocab, int64_t dim, int64_t n_idx,
+                    cudaStream_t stream) {
+    const Q *table = static_cast<const Q *>(table_);
+    const T *scale = static_cast<const T *>(scale_);
+    const I *idx = static_cast<const I *>(idx_);
+    T *out = static_cast<T *>(out_);
+    constexpr int VEC = 16 / sizeof(T);
+    const bool vec_ok = (dim % VEC == 0) && aligned(out, 16) && aligned(table, VEC * sizeof(Q));
+    const int64_t total = n_idx * (vec_ok ? dim / VEC : dim);
+    int64_t blocks = ceil_div(total, kThreads);
+    const int64_t cap = (int64_t)sm_count() * 16;
+    if (cap > 0 && blocks > cap) blocks = cap;
+    if (blocks < 1) blocks = 1;
+    unsigned int *status = device_status_word();
+    if (vec_ok) {
+        embedding_dequant_kernel<T, Q, I, VEC><<<(unsigned)blocks, kThreads, 0, stream>>>(table, scale, idx, out, vocab, dim, n_idx, status);
+    } else {
+        embedding_dequant_kernel<T, Q, I, 1><<<(unsigned)blocks, kThreads, 0, stream>>>(table, scale, idx, out, vocab, dim, n_idx, status);
+    }
+    B200Q_CHECK_LAUNCH("embedding_dequant_kernel");
+    return B200Q_OK;
+}
+
 int check_common(const char *op, const void *a, const void *b, const void *c, int64_t rows, int64_t cols, int f_type,
                  int q_type, int reduce_dim) {
     if (rows < 0 || cols < 0) return set_error(B200Q_INVALID_ARGUMENT, "%s: negative shape [%lld, %lld]", op, (long long)rows, (long long)cols);
@@ -485,6 +543,29 @@ B200Q_API int b200q_symmetric_dequantize(const void *wq, const void *scale, void
         default: return B200Q_DISPATCH_DQ(float);
     }
 #undef B200Q_DISPATCH_DQ
+}
+
+B200Q_API int b200q_embedding_dequantize(const void *table, const void *scale, const void *indices, void *out, int64_t vocab,
+                                         int64_t dim, int64_t n_indices, int scale_type, int q_type, int index_bytes, void *stream) {
+    using namespace b200q;
+    int rc = check_common("embedding_dequantize", table, scale, table, vocab, dim, scale_type, q_type, 1);
+    if (rc != B200Q_OK) return rc;
+    if (n_indices < 0) return set_error(B200Q_INVALID_ARGUMENT, "embedding_dequantize: negative index count %lld", (long long)n_indices);
+    if (index_bytes != 4 && index_bytes != 8) return set_error(B200Q_INVALID_ARGUMENT, "embedding_dequantize: indices must be int32 or int64 (4 or 8 bytes), got %d", index_bytes);
+    if (n_indices == 0 || dim == 0) return B200Q_OK;
+    if (indices == nullptr || out == nullptr || table == nullptr || scale == nullptr) return set_error(B200Q_INVALID_ARGUMENT, "embedding_dequantize: null pointer argument");
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+#define B200Q_DISPATCH_E2(T, Q)                                                                                    \
+    (index_bytes == 8 ? embedding_typed<T, Q, int64_t>(table, scale, indices, out, vocab, dim, n_indices, s)      \
+                      : embedding_typed<T, Q, int32_t>(table, scale, indices, out, vocab, dim, n_indices, s))
+#define B200Q_DISPATCH_E(T) (q_type == B200Q_I8 ? B200Q_DISPATCH_E2(T, int8_t) : B200Q_DISPATCH_E2(T, int16_t))
+    switch (scale_type) {
+        case B200Q_F16: return B200Q_DISPATCH_E(__half);
+        case B200Q_BF16: return B200Q_DISPATCH_E(__nv_bfloat16);
+        default: return B200Q_DISPATCH_E(float);
+    }
+#undef B200Q_DISPATCH_E
+#undef B200Q_DISPATCH_E2
 }
 
 }  // extern "C"

@@ -125,6 +125,9 @@ B200Q_API int b200q_check_status(void) {
     if (v[0] == 0) return B200Q_OK;
     const unsigned int zero[2] = {0, 0};
     B200Q_CUDA_TRY(cudaMemcpy(word, zero, sizeof(zero), cudaMemcpyHostToDevice));
+    if ((v[0] & 0xbfffffffu) == 0) {
+        return b200q::set_error(B200Q_INVALID_ARGUMENT, "an embedding lookup met an index outside its table (that row was written as zeros)");
+    }
     return b200q::set_error(B200Q_KERNEL_TIMEOUT,
                             "a bounded device-side wait ran out: first in kernel id %u at wait site %u; all that ran out, or-ed: 0x%08x",
                             v[1] & 0xffu, (v[1] >> 8) & 0xffu, v[0]);

@@ -118,6 +118,11 @@ SIGNATURES = {
     'b200q_check_status': ([], c_int, True),
     'b200q_symmetric_quantize': ([c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int, c_int, c_int, c_void_p], c_int, True),
     'b200q_symmetric_dequantize': ([c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int, c_int, c_int, c_void_p], c_int, True),
+    'b200q_embedding_dequantize': (
+        [c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64, c_int, c_int, c_int, c_void_p],
+        c_int,
+        True,
+    ),
     'b200q_qlinear_workspace_bytes': ([c_int64, c_int64, c_int64, c_int], c_size_t, False),
     'b200q_qlinear_f16_i8': (
         [c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64, c_int, c_void_p, c_size_t, c_void_p],

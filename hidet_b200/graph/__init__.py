@@ -9,5 +9,17 @@ from .operators import (
     SymmetricQuantizedMatmulF16I8Op,
 )
 from .transforms import PassContext, ResolveRule, register_resolve_rule, SubgraphRewriteRule, optimize, resolve_operator
-from .patterns import default_patterns, symmetric_linear_patterns, SymmetricLinearQuantizePattern, quantized_matmul
+from .patterns import (
+    default_patterns,
+    symmetric_linear_patterns,
+    symmetric_embedding_quantize_patterns,
+    SymmetricLinearQuantizePattern,
+    SymmetricLinearQuantizePatternR,
+    SymmetricLinearQuantizePatternL,
+    SymmetricQuantizeMatmulFused,
+    SymmetricEmbeddingQuantizePattern,
+    quantized_matmul,
+    quantized_embedding,
+    dequantized_weight,
+)
 from .dynamo_backend import hidet_b200_backend, register

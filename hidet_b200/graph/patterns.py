@@ -21,7 +21,7 @@ import torch.fx as fx
 import torch.nn.functional as F
 
 from .. import quant
-from .operators import SymmetricQuantizedMatmulOp
+from .operators import SymmetricDeQuantizationOp, SymmetricQuantizedMatmulOp
 from .transforms import SubgraphRewriteRule
 
 
@@ -114,12 +114,143 @@ class SymmetricLinearQuantizePattern(SubgraphRewriteRule):
         return count
 
 
+# The reference's name for the rule with the constant on the right (linear.py:25-49).
+SymmetricLinearQuantizePatternR = SymmetricLinearQuantizePattern
+
+
+def dequantized_weight(wq: torch.Tensor, scale: torch.Tensor, dims=0) -> torch.Tensor:
+    """The call a two-step rewrite leaves in the graph: the dequantize operator."""
+    return SymmetricDeQuantizationOp(wq, scale, dims=dims).outputs[0]
+
+
+class SymmetricLinearQuantizePatternL(SubgraphRewriteRule):
+    """matmul(W, x) with a constant 2-D float16 W[M, K] => matmul(dequant(wq, scale, dims), x)
+    (python/hidet/graph/transforms/graph_patterns/quant/linear.py:52-84).  As in the reference, this
+    form keeps a plain matmul behind a dequantize (its fused rule only matches the constant on the
+    right, linear.py:87-124): the weight is stored in int8, the product is not fused."""
+
+    def __init__(self, quant_type: str = 'int8', dims: Union[int, List[int]] = 0):
+        super().__init__('symmetric_linear_quantize_left')
+        self.quant_type = quant_type
+        self.dims = dims
+
+    def apply(self, gm: fx.GraphModule, constants: Dict[str, torch.Tensor]) -> int:
+        count = 0
+        existing = sum(1 for name, _ in gm.named_buffers() if name.startswith('_b200q_lwq_'))
+        for node in list(gm.graph.nodes):
+            if node.op != 'call_function' or node.target not in _MATMULS or len(node.args) != 2:
+                continue
+            w, x = node.args
+            if not isinstance(w, fx.Node) or w.name not in constants or not _eligible(constants[w.name]):
+                continue
+            if isinstance(x, fx.Node) and x.name in constants:
+                continue  # both constant: nothing to gain
+            wq, scale = quant.symmetric_quantize(constants[w.name].contiguous(), self.quant_type, dims=self.dims)
+            wq_name, scale_name = '_b200q_lwq_{}'.format(existing + count), '_b200q_lscale_{}'.format(existing + count)
+            gm.register_buffer(wq_name, wq)
+            gm.register_buffer(scale_name, scale)
+            with gm.graph.inserting_before(node):
+                wd = gm.graph.call_function(dequantized_weight, (gm.graph.get_attr(wq_name), gm.graph.get_attr(scale_name)), {'dims': self.dims})
+                new = gm.graph.call_function(torch.matmul, (wd, x))
+            node.replace_all_uses_with(new)
+            gm.graph.erase_node(node)
+            count += 1
+        return count
+
+
+class SymmetricQuantizeMatmulFused(SubgraphRewriteRule):
+    """matmul(x, dequant(wq, scale, dims=0)) => symmetric_quant_matmul(x, wq, scale), under the conditions of
+    python/hidet/graph/transforms/graph_patterns/quant/linear.py:87-124 (int8 2-D weight, per-column scale,
+    last dimensions even / multiples of 4).  Serves graphs that were quantized in two steps."""
+
+    def __init__(self):
+        super().__init__('symmetric_quantize_matmul_fused')
+
+    def apply(self, gm: fx.GraphModule, constants: Dict[str, torch.Tensor]) -> int:
+        count = 0
+        for node in list(gm.graph.nodes):
+            if node.op != 'call_function' or node.target not in _MATMULS or len(node.args) != 2:
+                continue
+            x, wd = node.args
+            if not isinstance(wd, fx.Node) or wd.op != 'call_function' or wd.target is not dequantized_weight:
+                continue
+            if wd.kwargs.get('dims', wd.args[2] if len(wd.args) > 2 else 0) not in (0, [0]):
+                continue
+            wq_node, scale_node = wd.args[0], wd.args[1]
+            wq = constants.get(getattr(wq_node, 'name', None))
+            scale = constants.get(getattr(scale_node, 'name', None))
+            if wq is None or scale is None or wq.dtype != torch.int8 or wq.dim() != 2 or scale.dtype != torch.float16:
+                continue
+            if wq.shape[1] % 4 or wq.shape[0] % 2 or scale.shape[0] != wq.shape[1]:
+                continue
+            with gm.graph.inserting_before(node):
+                new = gm.graph.call_function(quantized_matmul, (x, wq_node, scale_node))
+            node.replace_all_uses_with(new)
+            gm.graph.erase_node(node)
+            count += 1
+        return count
+
+
+def quantized_embedding(indices: torch.Tensor, wq: torch.Tensor, scale: torch.Tensor) -> torch.Tensor:
+    """The call the rewritten graph makes for an embedding: lookup in the row-quantized table."""
+    return quant.symmetric_dequantize_take(wq, scale, indices)
+
+
+class SymmetricEmbeddingQuantizePattern(SubgraphRewriteRule):
+    """embedding(W, ind) with a constant 2-D table => lookup in the table quantized per row
+    (python/hidet/graph/transforms/graph_patterns/quant/embedding.py:22-39: take(dequant(wq, scale, dims=-1),
+    ind, axis=0), here as one kernel).  Matches torch.nn.Embedding leaf modules and F.embedding calls with
+    int32 / int64 indices and no padding / max-norm options."""
+
+    def __init__(self, quant_type: str = 'int8'):
+        super().__init__('symmetric_embedding_quantize')
+        self.quant_type = quant_type
+
+    def _install(self, gm: fx.GraphModule, node: fx.Node, table: torch.Tensor, idx: int):
+        wq, scale = quant.symmetric_quantize(table.contiguous(), self.quant_type, dims=-1)
+        wq_name, scale_name = '_b200q_emb_wq_{}'.format(idx), '_b200q_emb_scale_{}'.format(idx)
+        gm.register_buffer(wq_name, wq)
+        gm.register_buffer(scale_name, scale)
+        with gm.graph.inserting_before(node):
+            return gm.graph.get_attr(wq_name), gm.graph.get_attr(scale_name)
+
+    def apply(self, gm: fx.GraphModule, constants: Dict[str, torch.Tensor]) -> int:
+        count = 0
+        existing = sum(1 for name, _ in gm.named_buffers() if name.startswith('_b200q_emb_wq_'))
+        for node in list(gm.graph.nodes):
+            table, ind = None, None
+            if node.op == 'call_module':
+                mod = gm.get_submodule(node.target)
+                if isinstance(mod, torch.nn.Embedding) and mod.max_norm is None and not mod.sparse and len(node.args) == 1:
+                    table, ind = mod.weight.detach(), node.args[0]
+            elif node.op == 'call_function' and node.target is F.embedding:
+                w = node.args[1] if len(node.args) > 1 else node.kwargs.get('weight')
+                plain = all(node.kwargs.get(k) in (None, False, 2.0) for k in ('padding_idx', 'max_norm', 'norm_type', 'scale_grad_by_freq', 'sparse'))
+                if isinstance(w, fx.Node) and w.name in constants and len(node.args) <= 2 and plain:
+                    table, ind = constants[w.name], node.args[0]
+            if table is None or table.dim() != 2 or not table.is_cuda or table.dtype not in (torch.float16, torch.bfloat16, torch.float32):
+                continue
+            wq_node, scale_node = self._install(gm, node, table, existing + count)
+            with gm.graph.inserting_before(node):
+                new = gm.graph.call_function(quantized_embedding, (ind, wq_node, scale_node))
+            node.replace_all_uses_with(new)
+            gm.graph.erase_node(node)
+            count += 1
+        return count
+
+
 def symmetric_linear_patterns(quant_type: str = 'int8', dims: Union[int, List[int]] = 0) -> List[SubgraphRewriteRule]:
-    """python/hidet/graph/transforms/graph_patterns/quant/__init__.py:31-46"""
-    return [SymmetricLinearQuantizePattern(quant_type=quant_type, dims=dims)]
+    """python/hidet/graph/transforms/graph_patterns/quant/__init__.py:31-46 and linear.py:87-92: the rule for
+    the constant on the right, the rule for the constant on the left, and the fusion of a two-step graph."""
+    return [SymmetricLinearQuantizePatternR(quant_type=quant_type, dims=dims), SymmetricLinearQuantizePatternL(quant_type=quant_type, dims=dims),
+            SymmetricQuantizeMatmulFused()]
+
+
+def symmetric_embedding_quantize_patterns(quant_type: str = 'int8') -> List[SubgraphRewriteRule]:
+    """python/hidet/graph/transforms/graph_patterns/quant/embedding.py:42-43"""
+    return [SymmetricEmbeddingQuantizePattern(quant_type=quant_type)]
 
 
 def default_patterns() -> List[SubgraphRewriteRule]:
-    """python/hidet/graph/transforms/graph_patterns/quant/__init__.py:19-28 (the embedding rule of the
-    reference is outside this path)."""
-    return symmetric_linear_patterns(quant_type='int8', dims=0)
+    """python/hidet/graph/transforms/graph_patterns/quant/__init__.py:19-28: embedding tables and linear layers."""
+    return symmetric_embedding_quantize_patterns(quant_type='int8') + symmetric_linear_patterns(quant_type='int8', dims=0)

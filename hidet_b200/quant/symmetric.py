@@ -110,3 +110,30 @@ def symmetric_dequantize(wq: torch.Tensor, scale: torch.Tensor, dims: Union[int,
             current_stream_ptr(wq.device),
         )
     return w
+
+
+def symmetric_dequantize_take(wq: torch.Tensor, scale: torch.Tensor, indices: torch.Tensor) -> torch.Tensor:
+    """take(symmetric_dequantize(wq, scale, dims=-1), indices, axis=0) in one kernel: the lookup the
+    reference's embedding rule leaves in the graph (python/hidet/graph/transforms/graph_patterns/quant/
+    embedding.py:22-39), without materialising the dequantized table.  wq is int8 / int16 [vocab, dim]
+    quantized per row, scale [vocab]; indices are int32 or int64 of any shape; the result has shape
+    indices.shape + [dim] and scale's dtype, and equals the rows of the dequantized table bit for bit."""
+    require_cuda(wq, 'wq')
+    require_cuda(scale, 'scale')
+    require_cuda(indices, 'indices')
+    if wq.dim() != 2 or wq.dtype not in QUANT_CODES:
+        raise ValueError('expect a 2-D int8 or int16 table, got {} of shape {}'.format(wq.dtype, list(wq.shape)))
+    if scale.dtype not in FLOAT_CODES or list(scale.shape) != [wq.shape[0]]:
+        raise ValueError('scale has shape {}, expected [{}] (one scale per table row)'.format(list(scale.shape), wq.shape[0]))
+    if indices.dtype not in (torch.int32, torch.int64):
+        raise ValueError('indices must be int32 or int64, got {}'.format(indices.dtype))
+    wq = wq.contiguous()
+    scale = scale.contiguous()
+    idx = indices.contiguous()
+    out = torch.empty(list(indices.shape) + [wq.shape[1]], dtype=scale.dtype, device=wq.device)
+    with torch.cuda.device(wq.device):
+        ffi.func('b200q_embedding_dequantize')(
+            wq.data_ptr(), scale.data_ptr(), idx.data_ptr(), out.data_ptr(), wq.shape[0], wq.shape[1], idx.numel(),
+            FLOAT_CODES[scale.dtype], QUANT_CODES[wq.dtype], idx.element_size(), current_stream_ptr(wq.device),
+        )
+    return out

@@ -16,6 +16,15 @@
  *   - every entry point returns a b200q_status.  On failure a thread-local message is kept and
  *     b200q_get_last_error() returns it and clears it (read-and-clear, like
  *     hidet_get_last_error).  Nothing aborts the process and no kernel traps.
+ *   - the quantized-linear kernels are launched as programmatic dependents of the kernel in front of them
+ *     in the stream: they request `wq` and `scale` BEFORE the stream dependency on that kernel is
+ *     honoured (activations, outputs and scratch are touched only after it).  `wq` and `scale` must
+ *     therefore be complete when the kernel in front may let its dependents start.  Ordinary kernels
+ *     (every other kernel of this library, memcpy / memset nodes, anything that does not itself execute
+ *     griddepcontrol.launch_dependents) let dependents start only when they have finished, so producing a
+ *     weight with b200q_symmetric_quantize and using it in the next call on the same stream is safe.  Not
+ *     safe: writing `wq` or `scale` from a kernel that triggers its dependents early, directly in front of
+ *     a quantized linear on the same stream; put an event or any ordinary kernel between the two.
  *   - matrices are dense row-major.  "KN" weight layout = [K, N] with N contiguous, the layout of
  *     the reference operator (python/hidet/graph/ops/quant/matmul.py:30-32); "NK" = [N, K] with K
  *     contiguous, the layout torch.nn.Linear stores.
@@ -87,6 +96,20 @@ B200Q_API int b200q_symmetric_quantize(const void *w, void *wq, void *scale, int
 B200Q_API int b200q_symmetric_dequantize(const void *wq, const void *scale, void *w, int64_t rows, int64_t cols,
                                          int scale_type /* b200q_float_type */, int q_type /* b200q_quant_type */,
                                          int reduce_dim, void *stream);
+
+/*
+ * Embedding lookup in a row-quantized table: out[i, :] = (scale_type) table[indices[i], :] * scale[indices[i]]
+ * for table int8 / int16 [vocab, dim] quantized per row (b200q_symmetric_quantize with reduce_dim = 1) and
+ * scale [vocab].  Replaces take(symmetric_dequantize(wq, scale, dims=-1), indices, axis=0), the graph the
+ * reference's embedding rule builds (python/hidet/graph/transforms/graph_patterns/quant/embedding.py:22-39),
+ * without materialising the dequantized table; every output row equals the row of the dequantized table
+ * bit for bit.  index_bytes is 4 (int32) or 8 (int64), the index types the reference's rule accepts; a
+ * negative index counts from the end; an index outside the table yields a row of zeros and is reported
+ * by b200q_check_status.
+ */
+B200Q_API int b200q_embedding_dequantize(const void *table, const void *scale, const void *indices, void *out, int64_t vocab,
+                                         int64_t dim, int64_t n_indices, int scale_type /* b200q_float_type */,
+                                         int q_type /* b200q_quant_type */, int index_bytes, void *stream);
 
 /*
  * Bytes of scratch b200q_qlinear_f16_i8 needs for this problem (0 is a valid answer).

@@ -57,6 +57,15 @@ CASES = [
     ('qmm_f16_i8_16x4096x4096', 'matmul_f16_i8', {'m': 16, 'k': 4096, 'n': 4096}),
     ('qmm_f16_i8_1x4096x11008', 'matmul_f16_i8', {'m': 1, 'k': 4096, 'n': 11008}),
     ('qmm_generic_4x512x256', 'matmul_generic', {'m': 4, 'k': 512, 'n': 256}),
+    # the other types the reference's own tests run (tests/operators_core/test_symmetric_quant.py:19-26,
+    # tests/operators_core/test_quantization.py:21-36): int16 codes, bfloat16 weights
+    ('quant_f16_i16_d0_200x48', 'quantize', {'rows': 200, 'cols': 48, 'dims': 0, 'qtype': 'int16'}),
+    ('quant_f16_i16_d1_512x384', 'quantize', {'rows': 512, 'cols': 384, 'dims': -1, 'qtype': 'int16'}),
+    ('quant_bf16_d0_200x48', 'quantize', {'rows': 200, 'cols': 48, 'dims': 0, 'wtype': 'bfloat16'}),
+    ('quant_bf16_d1_512x384', 'quantize', {'rows': 512, 'cols': 384, 'dims': -1, 'wtype': 'bfloat16'}),
+    ('quant_bf16_d0_4096x4096', 'quantize', {'rows': 4096, 'cols': 4096, 'dims': 0, 'wtype': 'bfloat16'}),
+    ('dequant_f16_i16_d0_200x48', 'dequantize', {'rows': 200, 'cols': 48, 'dims': 0, 'qtype': 'int16'}),
+    ('dequant_bf16_d0_200x48', 'dequantize', {'rows': 200, 'cols': 48, 'dims': 0, 'wtype': 'bfloat16'}),
 ]
 
 
@@ -110,11 +119,12 @@ def generate_sources(ref: str, scratch: str) -> dict:
     target = Target.from_string('cuda')
     sources = {}
     for name, kind, p in CASES:
+        wtype, qtype = p.get('wtype', 'float16'), p.get('qtype', 'int8')
         if kind == 'quantize':
-            task = SymmetricQuantizationTask(tensor_input('w', 'float16', [p['rows'], p['cols']]), dtypes.int8, dims=p['dims'])
+            task = SymmetricQuantizationTask(tensor_input('w', wtype, [p['rows'], p['cols']]), getattr(dtypes, qtype), dims=p['dims'])
         elif kind == 'dequantize':
             scale_len = p['cols'] if p['dims'] == 0 else p['rows']
-            task = SymmetricDeQuantizationTask(tensor_input('wq', 'int8', [p['rows'], p['cols']]), tensor_input('scale', 'float16', [scale_len]), dims=p['dims'])
+            task = SymmetricDeQuantizationTask(tensor_input('wq', qtype, [p['rows'], p['cols']]), tensor_input('scale', wtype, [scale_len]), dims=p['dims'])
         elif kind == 'matmul_f16_i8':
             task = SymmetricQuantizedMatmulF16I8Task(tensor_input('a', 'float16', [p['m'], p['k']]), tensor_input('b', 'int8', [p['k'], p['n']]),
                                                      tensor_input('scale', 'float16', [p['n']]), 1)

@@ -56,9 +56,11 @@ class ReferenceKernels:
             self.runtime.register_callback(name, ctypes.cast(cb, ctypes.c_void_p))
         self.runtime.use_torch_cuda_stream(False)
 
+    _DEFAULTS = {'wtype': 'float16', 'qtype': 'int8'}
+
     def find(self, kind: str, **params) -> Optional[str]:
         for c in self.manifest['cases']:
-            if c['kind'] == kind and all(c.get(k) == v for k, v in params.items()):
+            if c['kind'] == kind and all(c.get(k, self._DEFAULTS.get(k)) == v for k, v in params.items()):
                 return c['name']
         return None
 
@@ -79,24 +81,27 @@ class ReferenceKernels:
         torch.cuda.current_stream().synchronize()
 
     # ---- the operators of the path, by the reference's names ----
-    def symmetric_quantize(self, w, dims: int) -> Tuple['torch.Tensor', 'torch.Tensor']:
+    def symmetric_quantize(self, w, dims: int, quant_type: str = 'int8') -> Tuple['torch.Tensor', 'torch.Tensor']:
         torch = self.torch
         rows, cols = w.shape
-        name = self.find('quantize', rows=rows, cols=cols, dims=dims)
+        wtype = {torch.float16: 'float16', torch.bfloat16: 'bfloat16'}[w.dtype]
+        name = self.find('quantize', rows=rows, cols=cols, dims=dims, wtype=wtype, qtype=quant_type)
         if name is None:
-            raise KeyError('no reference kernel was built for quantize {}x{} dims={}'.format(rows, cols, dims))
-        wq = torch.empty(rows, cols, dtype=torch.int8, device='cuda')
-        scale = torch.empty(cols if dims == 0 else rows, dtype=torch.float16, device='cuda')
+            raise KeyError('no reference kernel was built for quantize {} -> {} {}x{} dims={}'.format(wtype, quant_type, rows, cols, dims))
+        wq = torch.empty(rows, cols, dtype=getattr(torch, quant_type), device='cuda')
+        scale = torch.empty(cols if dims == 0 else rows, dtype=w.dtype, device='cuda')
         self.launch(name, w, wq, scale)
         return wq, scale
 
     def symmetric_dequantize(self, wq, scale, dims: int):
         torch = self.torch
         rows, cols = wq.shape
-        name = self.find('dequantize', rows=rows, cols=cols, dims=dims)
+        wtype = {torch.float16: 'float16', torch.bfloat16: 'bfloat16'}[scale.dtype]
+        qtype = {torch.int8: 'int8', torch.int16: 'int16'}[wq.dtype]
+        name = self.find('dequantize', rows=rows, cols=cols, dims=dims, wtype=wtype, qtype=qtype)
         if name is None:
-            raise KeyError('no reference kernel was built for dequantize {}x{} dims={}'.format(rows, cols, dims))
-        w = torch.empty(rows, cols, dtype=torch.float16, device='cuda')
+            raise KeyError('no reference kernel was built for dequantize {} {} {}x{} dims={}'.format(wtype, qtype, rows, cols, dims))
+        w = torch.empty(rows, cols, dtype=scale.dtype, device='cuda')
         self.launch(name, wq, scale, w)
         return w
 

@@ -92,6 +92,62 @@ def test_quantization_pass_rewrites_matmul_and_linear():
     assert torch.equal(got, manual)
 
 
+class LeftConstant(nn.Module):
+    def __init__(self):
+        super().__init__()
+        g = torch.Generator().manual_seed(7)
+        self.w = nn.Parameter((torch.randn(96, 256, generator=g) * 0.02).half())   # W[M, K] on the left
+
+    def forward(self, x):
+        return torch.matmul(self.w, x)
+
+
+def test_constant_on_the_left_is_stored_in_int8_behind_a_dequantize():
+    """The reference's rule for matmul(W, x) (graph_patterns/quant/linear.py:52-84) keeps a plain matmul behind a
+    dequantize, and its fused rule does not match that side."""
+    model = LeftConstant().cuda().eval()
+    x = torch.randn(256, 40, generator=torch.Generator().manual_seed(8)).half().cuda()
+    want = model(x)
+    gm = fx.symbolic_trace(model)
+    with hg.PassContext() as ctx:
+        ctx.set_precision('int8')
+        hg.optimize(gm)
+    targets = [n.target for n in gm.graph.nodes if n.op == 'call_function']
+    assert targets.count(hg.dequantized_weight) == 1 and targets.count(torch.matmul) == 1 and hg.quantized_matmul not in targets
+    buffers = dict(gm.named_buffers())
+    assert buffers['_b200q_lwq_0'].dtype == torch.int8 and tuple(buffers['_b200q_lscale_0'].shape) == (256,)   # dims=0: one scale per column of W
+    got = gm(x)
+    wq, scale = hidet_b200.symmetric_quantize(model.w.detach(), 'int8', dims=0)
+    assert torch.equal(got, torch.matmul(hidet_b200.symmetric_dequantize(wq, scale, dims=0), x))
+    assert torch.allclose(got.float(), want.float(), atol=2e-1, rtol=2e-1)
+
+
+def test_two_step_graph_is_fused():
+    """matmul(x, dequant(wq, scale)) => symmetric_quant_matmul(x, wq, scale) (graph_patterns/quant/linear.py:87-124)."""
+    g = torch.Generator().manual_seed(9)
+    w = (torch.randn(256, 128, generator=g) * 0.02).half().cuda()
+    wq, scale = hidet_b200.symmetric_quantize(w, 'int8', dims=0)
+
+    holder = nn.Module()
+    holder.register_buffer('wq', wq)
+    holder.register_buffer('scale', scale)
+    graph = fx.Graph()
+    x_node = graph.placeholder('x')
+    wd = graph.call_function(hg.dequantized_weight, (graph.get_attr('wq'), graph.get_attr('scale')), {'dims': 0})
+    graph.output(graph.call_function(torch.matmul, (x_node, wd)))
+    gm = fx.GraphModule(holder, graph)
+    x = torch.randn(5, 256, generator=g).half().cuda()
+    unfused = gm(x)
+    with hg.PassContext() as ctx:
+        ctx.add_quantize_rules([hg.SymmetricQuantizeMatmulFused()])
+        hg.optimize(gm)
+    targets = [n.target for n in gm.graph.nodes if n.op == 'call_function']
+    assert targets == [hg.quantized_matmul]
+    fused = gm(x)
+    assert torch.equal(fused, hidet_b200.symmetric_quant_matmul(x, wq, scale))
+    assert torch.allclose(fused.float(), unfused.float(), atol=1e-2, rtol=1e-2)
+
+
 def test_pass_without_int8_leaves_the_graph_alone():
     model = TwoLinears().half().cuda().eval()
     gm = fx.symbolic_trace(model)

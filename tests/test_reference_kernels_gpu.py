@@ -76,6 +76,26 @@ def test_dequantize_matches_the_reference_kernels_bit_for_bit(ref, rows, cols):
         assert np.array_equal(got_o.view(np.int16), bits(want).cpu().numpy())
 
 
+@pytest.mark.parametrize('rows,cols,dims,wtype,qtype,kind', [
+    (200, 48, 0, 'float16', 'int16', 'seeded'), (200, 48, 0, 'float16', 'int16', 'adversarial'), (512, 384, -1, 'float16', 'int16', 'seeded'),
+    (200, 48, 0, 'bfloat16', 'int8', 'seeded'), (200, 48, 0, 'bfloat16', 'int8', 'adversarial'), (512, 384, -1, 'bfloat16', 'int8', 'seeded'),
+    (4096, 4096, 0, 'bfloat16', 'int8', 'seeded'),
+])
+def test_int16_codes_and_bfloat16_weights_match_the_reference_kernels_bit_for_bit(ref, rows, cols, dims, wtype, qtype, kind):
+    """The other types the reference's tests run (tests/operators_core/test_symmetric_quant.py:19-26)."""
+    w_np = adversarial(rows, cols, seed=rows + cols) if kind == 'adversarial' else seeded_weight(rows, cols, seed=rows + cols)
+    w = torch.from_numpy(w_np).cuda().to(getattr(torch, wtype))
+    wq_ref, scale_ref = ref.symmetric_quantize(w, dims, qtype)
+    wq, scale = hidet_b200.symmetric_quantize(w, qtype, dims=dims)
+    assert wq.dtype == wq_ref.dtype and scale.dtype == scale_ref.dtype
+    assert torch.equal(bits(scale), bits(scale_ref)), '{} scale words differ'.format(int((bits(scale) != bits(scale_ref)).sum()))
+    assert torch.equal(wq, wq_ref), '{} of {} codes differ'.format(int((wq != wq_ref).sum()), wq.numel())
+    if (rows, cols, dims) == (200, 48, 0):
+        want = ref.symmetric_dequantize(wq, scale, 0)
+        got = hidet_b200.symmetric_dequantize(wq, scale, dims=0)
+        assert torch.equal(bits(got), bits(want))
+
+
 @pytest.mark.parametrize('m,k,n,kind', [(16, 4096, 4096, 'matmul_f16_i8'), (1, 4096, 11008, 'matmul_f16_i8'), (4, 512, 256, 'matmul_generic')])
 def test_quantized_matmul_is_within_tolerance_of_the_reference_kernels(ref, m, k, n, kind):
     w = torch.from_numpy(seeded_weight(k, n, seed=k + n)).cuda()

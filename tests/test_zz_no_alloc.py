@@ -6,9 +6,6 @@ therefore cannot give the kernel a workspace, nor call cudaMalloc.  For them the
 fixed 512 KiB scratch array.  This test calls that entry point through the C ABI, on shapes that really
 use the scratch, twice in a row, and compares with the regular entry point, which gets a
 caller-allocated workspace.  Both run the same deterministic kernel, so the outputs must be identical.
-
-The file name sorts last on purpose: a run that stops at the first failure has then already run every
-other test.
 """
 import pytest
 import torch
@@ -52,6 +49,16 @@ def test_static_entry_point_matches_the_regular_one_twice(m, n, k):
     _static_call(a, wq, scale, out)
     assert torch.equal(out, want)
     assert ffi.func('b200q_check_status')() == ffi.OK
+
+
+def test_static_entry_point_with_an_empty_sum_writes_zeros_like_the_regular_one():
+    a = torch.zeros(3, 0, dtype=torch.float16, device='cuda')
+    wq = torch.zeros(0, 64, dtype=torch.int8, device='cuda')
+    scale = torch.ones(64, dtype=torch.float16, device='cuda')
+    out = torch.full((3, 64), 5.0, dtype=torch.float16, device='cuda')
+    ffi.func('b200q_qlinear_f16_i8_static')(0, 0, scale.data_ptr(), out.data_ptr(), 3, 64, 0, ffi.LAYOUT_KN, torch.cuda.current_stream().cuda_stream)
+    torch.cuda.synchronize()
+    assert not out.any()
 
 
 def test_static_entry_point_uses_scratch_on_these_shapes():
