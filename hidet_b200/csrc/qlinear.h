@@ -19,6 +19,20 @@ struct OutTargets {
     int64_t col0;  // first destination column
 };
 
+// What a kernel does to the scaled fp32 sums y[m, n] before the one rounding to f16:
+//   y += bias[n];  activation (silu_mul: the weight's columns come in pairs (gate_j, up_j) = (2j, 2j + 1), and
+//   z[m, j] = silu(y[m, 2j]) * y[m, 2j + 1] is the result, half as wide);  z += residual[m, j].
+// Takes the place of the element-wise operators the reference fuses into its matmul by IR rewriting
+// (python/hidet/graph/transforms/fuse_operator.py, python/hidet/graph/ops/quant/matmul_f16_i8.py:95-99).
+constexpr int kActNone = 0;
+constexpr int kActSiluMul = 1;
+struct Epilogue {
+    const void *bias = nullptr;      // f16 [N]
+    const void *residual = nullptr;  // f16 [M, ldr]
+    int64_t ldr = 0;                 // elements between rows of residual
+    int act = kActNone;
+};
+
 // How the small-M kernel splits a problem over CTAs, and the scratch that split needs.
 struct DecodePlan {
     int n_tiles = 0;
@@ -39,12 +53,12 @@ bool decode_kn_supported(const void *a, const void *wq, int64_t N, int64_t K);
 // c[M, N] = scale * (a[:, k_begin:k_end] x wq[k_begin:k_end, :]).  K is the row length of `a`.
 int launch_decode_kn(const void *a, const void *wq, const void *scale, void *c, int64_t M, int64_t N, int64_t K,
                      int64_t k_begin, int64_t k_end, bool allow_split, void *workspace, size_t workspace_bytes,
-                     cudaStream_t stream, const OutTargets *targets = nullptr);
+                     cudaStream_t stream, const OutTargets *targets = nullptr, const Epilogue *epilogue = nullptr);
 
 // The tensor-memory kernel for large M: same operand requirements as the small-M kernel.
 bool prefill_kn_supported(const void *a, const void *wq, int64_t N, int64_t K);
 int launch_prefill_kn(const void *a, const void *wq, const void *scale, void *c, int64_t M, int64_t N, int64_t K,
-                      cudaStream_t stream, const OutTargets *targets = nullptr);
+                      cudaStream_t stream, const OutTargets *targets = nullptr, const Epilogue *epilogue = nullptr);
 
 // Which kernel serves M activation rows.  The tensor-memory kernel's tiles span 64 or 256 rows and it
 // streams every weight tile once per row block; the small-M kernel re-streams the weight once per 16

@@ -85,6 +85,36 @@ B200Q_API int b200q_qlinear_f16_i8(const void *a, const void *wq, const void *sc
     return launch_generic(a, wq, scale, c, M, N, K, 0, K, w_layout, s);
 }
 
+B200Q_API int b200q_qlinear_f16_i8_fused(const void *a, const void *wq, const void *scale, void *c, int64_t M, int64_t N, int64_t K,
+                                         int w_layout, const b200q_epilogue *epilogue, void *workspace, size_t workspace_bytes, void *stream) {
+    using namespace b200q;
+    if (epilogue == nullptr) return b200q_qlinear_f16_i8(a, wq, scale, c, M, N, K, w_layout, workspace, workspace_bytes, stream);
+    int rc = check_qlinear_args("qlinear_f16_i8_fused", a, wq, scale, c, M, N, K, w_layout);
+    if (rc != B200Q_OK) return rc;
+    if (epilogue->activation != B200Q_ACT_NONE && epilogue->activation != B200Q_ACT_SILU_MUL) {
+        return set_error(B200Q_INVALID_ARGUMENT, "qlinear_f16_i8_fused: unknown activation %d", epilogue->activation);
+    }
+    const bool pairs = epilogue->activation == B200Q_ACT_SILU_MUL;
+    if (pairs && N % 2 != 0) return set_error(B200Q_INVALID_ARGUMENT, "qlinear_f16_i8_fused: the gate / up pairing needs an even N, got %lld", (long long)N);
+    const int64_t n_out = pairs ? N / 2 : N;
+    if (epilogue->residual != nullptr && epilogue->ldr < n_out) {
+        return set_error(B200Q_INVALID_ARGUMENT, "qlinear_f16_i8_fused: residual rows of %lld elements are shorter than the result's %lld", (long long)epilogue->ldr, (long long)n_out);
+    }
+    if (M == 0 || N == 0) return B200Q_OK;
+    if (w_layout != B200Q_LAYOUT_KN || K == 0 || !decode_kn_supported(a, wq, N, K)) {
+        return set_error(B200Q_UNSUPPORTED, "qlinear_f16_i8_fused: the fused epilogue is served for [K, N] weights with 16-byte aligned bases and rows "
+                                            "(N %% 16 == 0, K %% 8 == 0, K > 0); got layout %d N=%lld K=%lld", w_layout, (long long)N, (long long)K);
+    }
+    Epilogue ep;
+    ep.bias = epilogue->bias;
+    ep.residual = epilogue->residual;
+    ep.ldr = epilogue->ldr;
+    ep.act = pairs ? kActSiluMul : kActNone;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    if (use_prefill_kernel(M, N, K)) return launch_prefill_kn(a, wq, scale, c, M, N, K, s, nullptr, &ep);
+    return launch_decode_kn(a, wq, scale, c, M, N, K, 0, K, true, workspace, workspace_bytes, s, nullptr, &ep);
+}
+
 B200Q_API int b200q_qlinear_f16_i8_to_peers(const void *a, const void *wq, const void *scale, void *const *dst, int n_dst,
                                             int64_t ldc, int64_t col_offset, int64_t M, int64_t N, int64_t K, void *workspace,
                                             size_t workspace_bytes, void *stream) {

@@ -150,9 +150,29 @@ __device__ __forceinline__ void store_out(const OutTargets &o, int row, int col,
     for (int i = 0; i < o.count; ++i) static_cast<__half *>(o.ptr[i])[off] = v;
 }
 
+__device__ __forceinline__ float silu(float x) { return x / (1.0f + __expf(-x)); }
+
+// The end of every path: y is the scaled fp32 sum of column nn (in range or not), row `row`.  Adds the bias,
+// applies the activation (the value of the partner column nn ^ 1 sits in lane ^ partner_xor; every lane
+// of the calling warp that is active takes part), adds the residual, rounds once and stores.
+__device__ __forceinline__ void finish(const OutTargets &o, const Epilogue &ep, int row, int nn, int n_limit, bool valid, float y, int partner_xor) {
+    if (valid && ep.bias != nullptr) y += __half2float(__ldg(static_cast<const __half *>(ep.bias) + nn));
+    int col = nn;
+    if (ep.act == kActSiluMul) {
+        const float other = __shfl_xor_sync(__activemask(), y, partner_xor);
+        if (nn & 1) valid = false;  // the even column of a pair finishes both
+        y = silu(y) * other;
+        col = nn >> 1;
+    }
+    if (!valid || nn >= n_limit) return;
+    if (ep.residual != nullptr) y += __half2float(__ldg(static_cast<const __half *>(ep.residual) + (size_t)row * ep.ldr + col));
+    store_out(o, row, col, __float2half_rn(y));
+}
+
 struct Params {
     const __half *scale;
     OutTargets out;
+    Epilogue ep;
     float *partial;           // [groups][M][N] fp32 in the workspace, used when groups > 1
     unsigned int *counters;   // [m_tiles * n_tiles * cluster] in the workspace, zero on entry, zero on exit
     unsigned int *status;
@@ -332,16 +352,14 @@ __global__ void __launch_bounds__(THREADS) qlinear_decode_kn_kernel(const __grid
 #pragma unroll
                 for (int h = 0; h < 2; ++h) {
                     const int nn = n0 + col_base + 16 * j + 8 * h;
-                    if (nn < p.N) {
-                        const float sc = __half2float(p.scale[nn]);
+                    const float sc = nn < p.N ? __half2float(p.scale[nn]) : 0.0f;
 #pragma unroll
-                        for (int mt = 0; mt < MT; ++mt)
+                    for (int mt = 0; mt < MT; ++mt)
 #pragma unroll
-                            for (int e = 0; e < 2; ++e) {
-                                const int r = 8 * mt + 2 * t + e;
-                                if (r < rows) store_out(p.out, m0 + r, nn, __float2half_rn(acc[j][mt][2 * h + e] * sc));
-                            }
-                    }
+                        for (int e = 0; e < 2; ++e) {
+                            const int r = 8 * mt + 2 * t + e;  // columns nn and nn ^ 1 live in lanes that differ in g by one
+                            finish(p.out, p.ep, m0 + r, nn, p.N, r < rows, acc[j][mt][2 * h + e] * sc, 4);
+                        }
                 }
         }
         return;
@@ -418,10 +436,9 @@ __global__ void __launch_bounds__(THREADS) qlinear_decode_kn_kernel(const __grid
             const int r = idx / cols_per;
             const int cc = idx - r * cols_per;
             const int nn = col_first + cc;
-            if (nn < p.N && cc < own_cols) {
-                const float sc = idx < THREADS ? sc_own : __half2float(p.scale[nn]);
-                store_out(p.out, m0 + r, nn, __float2half_rn(sum_ranks(r, cc) * sc));
-            }
+            const bool valid = nn < p.N && cc < own_cols;  // N and own_cols are even: the two columns of a pair agree
+            const float sc = idx < THREADS ? sc_own : (valid ? __half2float(p.scale[nn]) : 0.0f);
+            finish(p.out, p.ep, m0 + r, nn, p.N, valid, valid ? sum_ranks(r, cc) * sc : 0.0f, 1);
         }
         return;
     }
@@ -450,12 +467,14 @@ __global__ void __launch_bounds__(THREADS) qlinear_decode_kn_kernel(const __grid
         const int r = idx / cols_per;
         const int cc = idx - r * cols_per;
         const int nn = col_first + cc;
-        if (nn < p.N && cc < own_cols) {
-            float v = 0.0f;
+        const bool valid = nn < p.N && cc < own_cols;
+        float v = 0.0f;
+        if (valid) {
 #pragma unroll 4
             for (int gr = 0; gr < p.groups; ++gr) v += __ldcg(&p.partial[((size_t)gr * p.M + (m0 + r)) * p.N + nn]);
-            store_out(p.out, m0 + r, nn, __float2half_rn(v * (idx < THREADS ? sc_own : __half2float(p.scale[nn]))));
+            v *= idx < THREADS ? sc_own : __half2float(p.scale[nn]);
         }
+        finish(p.out, p.ep, m0 + r, nn, p.N, valid, v, 1);
     }
     if (threadIdx.x == 0) p.counters[slot] = 0;  // leave the workspace ready for the next call
 }
@@ -503,7 +522,7 @@ bool decode_kn_supported(const void *a, const void *wq, int64_t N, int64_t K) {
 
 int launch_decode_kn(const void *a, const void *wq, const void *scale, void *c, int64_t M, int64_t N, int64_t K,
                      int64_t k_begin, int64_t k_end, bool allow_split, void *workspace, size_t workspace_bytes,
-                     cudaStream_t stream, const OutTargets *targets) {
+                     cudaStream_t stream, const OutTargets *targets, const Epilogue *epilogue) {
     using namespace decode;
     DecodePlan pl = plan_decode(M, N, k_end - k_begin);
     if (!allow_split) {
@@ -535,9 +554,10 @@ int launch_decode_kn(const void *a, const void *wq, const void *scale, void *c, 
     } else {
         p.out.ptr[0] = c;
         p.out.count = 1;
-        p.out.ldc = N;
+        p.out.ldc = (epilogue != nullptr && epilogue->act == kActSiluMul) ? N / 2 : N;
         p.out.col0 = 0;
     }
+    if (epilogue != nullptr) p.ep = *epilogue;
     p.counters = static_cast<unsigned int *>(workspace);
     p.partial = pl.partial_bytes > 0 ? reinterpret_cast<float *>(static_cast<unsigned char *>(workspace) + pl.counter_bytes) : nullptr;
     p.status = device_status_word();

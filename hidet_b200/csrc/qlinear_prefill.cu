@@ -136,12 +136,14 @@ __device__ __forceinline__ void cvt_s8x4_to_f16_pairs(uint32_t v, uint32_t &p01,
 struct Params {
     const __half *scale;
     OutTargets out;
+    Epilogue ep;
     unsigned int *status;
     int M, N, K;
     int n_tiles, m_tiles;
 };
 
-template <int TM>
+// FUSED: the epilogue of p.ep (bias, gate / up pairing, residual) is compiled in.
+template <int TM, bool FUSED>
 __global__ void __launch_bounds__(THREADS, 1) qlinear_prefill_kn_kernel(const __grid_constant__ CUtensorMap map_w,
                                                                         const __grid_constant__ CUtensorMap map_a,
                                                                         const Params p) {
@@ -351,18 +353,34 @@ __global__ void __launch_bounds__(THREADS, 1) qlinear_prefill_kn_kernel(const __
             tc_fence_after_sync();
             const int n = n0 + 32 * q + lane;
             const float sc = n < p.N ? __half2float(p.scale[n]) : 0.0f;
+            const float bias = (FUSED && n < p.N && p.ep.bias != nullptr) ? __half2float(__ldg(static_cast<const __half *>(p.ep.bias) + n)) : 0.0f;
+            const bool pairs = FUSED && p.ep.act == kActSiluMul;  // columns (2j, 2j + 1) = (gate, up): the even lane finishes both
+            const int out_n = pairs ? p.N >> 1 : p.N;    // width of the result
+            const int out_n0 = pairs ? n0 >> 1 : n0;     // first result column of this tile
+            const int out_col = pairs ? n >> 1 : n;      // this lane's result column
+            const bool writer = n < p.N && !(pairs && (lane & 1));
+            const __half *res = FUSED ? static_cast<const __half *>(p.ep.residual) : nullptr;
             const int m_left = p.M - m0;
-            const bool cols_ok = n0 + chunk * 8 < p.N;  // N is a multiple of 16: eight columns are in or out together
-            const size_t col_off = (size_t)p.out.col0 + n0 + chunk * 8;
+            const bool cols_ok = out_n0 + chunk * 8 < out_n && !(pairs && chunk >= 8);  // widths are multiples of 8: eight columns are in or out together
+            const size_t col_off = (size_t)p.out.col0 + out_n0 + chunk * 8;
 #pragma unroll 1
             for (int cb = 0; cb < TM / 32; ++cb) {
                 if (cb * 32 >= m_left) break;  // rows beyond M: nothing to store (uniform across the four warps)
                 uint32_t v[32];
                 tmem_ld_32x32(tmem_base + ((uint32_t)(32 * q) << 16) + buf * TM + cb * 32, v);
                 tmem_ld_wait();
-                __half *col = reinterpret_cast<__half *>(staging) + 32 * q + lane;
+                __half *col = reinterpret_cast<__half *>(staging) + (pairs ? (32 * q + lane) >> 1 : 32 * q + lane);
 #pragma unroll
-                for (int j = 0; j < 32; ++j) col[j * (STAGE_ROW_BYTES / 2)] = __float2half_rn(__uint_as_float(v[j]) * sc);
+                for (int j = 0; j < 32; ++j) {
+                    float y = __uint_as_float(v[j]) * sc;
+                    if (FUSED) y += bias;
+                    if (pairs) {
+                        const float up = __shfl_xor_sync(0xffffffffu, y, 1);
+                        y = y / (1.0f + __expf(-y)) * up;
+                    }
+                    if (res != nullptr && writer && cb * 32 + j < m_left) y += __half2float(__ldg(res + (size_t)(m0 + cb * 32 + j) * p.ep.ldr + out_col));
+                    if (writer) col[j * (STAGE_ROW_BYTES / 2)] = __float2half_rn(y);
+                }
                 asm volatile("bar.sync 1, 128;" ::: "memory");  // the four epilogue warps: block complete
 #pragma unroll
                 for (int pass = 0; pass < 4; ++pass) {
@@ -419,7 +437,7 @@ static int choose_tile_m(int64_t M, int64_t N, int sms) {
 
 template <int TM>
 static int launch_prefill_tm(const void *a, const void *wq, const void *scale, void *c, int64_t M, int64_t N, int64_t K,
-                             cudaStream_t stream, const OutTargets *targets, int sms) {
+                             cudaStream_t stream, const OutTargets *targets, const Epilogue *epilogue, int sms) {
     using namespace prefill;
     using Cfg = Config<TM>;
     CUtensorMap map_w, map_a;
@@ -437,9 +455,11 @@ static int launch_prefill_tm(const void *a, const void *wq, const void *scale, v
     } else {
         p.out.ptr[0] = c;
         p.out.count = 1;
-        p.out.ldc = N;
+        p.out.ldc = (epilogue != nullptr && epilogue->act == kActSiluMul) ? N / 2 : N;
         p.out.col0 = 0;
     }
+    if (epilogue != nullptr) p.ep = *epilogue;
+    if (p.ep.act == kActSiluMul && N % 16 != 0) return set_error(B200Q_INVALID_ARGUMENT, "qlinear: the gate / up pairing needs N to be a multiple of 16, got %lld", (long long)N);
     if (p.out.count != 1) return set_error(B200Q_UNSUPPORTED, "qlinear: the large-M kernel stores to one destination, got %d", p.out.count);
     if ((reinterpret_cast<uintptr_t>(p.out.ptr[0]) & 15u) != 0) return set_error(B200Q_INVALID_ARGUMENT, "qlinear: output is not 16-byte aligned");
     if (p.out.ldc % 8 != 0 || p.out.col0 % 8 != 0) return set_error(B200Q_INVALID_ARGUMENT, "qlinear: output row length and column offset must be multiples of 8 elements");
@@ -457,21 +477,26 @@ static int launch_prefill_tm(const void *a, const void *wq, const void *scale, v
     int dev = 0;
     B200Q_CUDA_TRY(cudaGetDevice(&dev));
     if (dev < 0 || dev >= 64 || !attr_set[dev]) {
-        B200Q_CUDA_TRY(cudaFuncSetAttribute(qlinear_prefill_kn_kernel<TM>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES));
+        B200Q_CUDA_TRY(cudaFuncSetAttribute(qlinear_prefill_kn_kernel<TM, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES));
+        B200Q_CUDA_TRY(cudaFuncSetAttribute(qlinear_prefill_kn_kernel<TM, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES));
         if (dev >= 0 && dev < 64) attr_set[dev] = true;
     }
-    qlinear_prefill_kn_kernel<TM><<<grid, THREADS, Cfg::SMEM_BYTES, stream>>>(map_w, map_a, p);
+    if (p.ep.bias != nullptr || p.ep.residual != nullptr || p.ep.act != kActNone) {
+        qlinear_prefill_kn_kernel<TM, true><<<grid, THREADS, Cfg::SMEM_BYTES, stream>>>(map_w, map_a, p);
+    } else {
+        qlinear_prefill_kn_kernel<TM, false><<<grid, THREADS, Cfg::SMEM_BYTES, stream>>>(map_w, map_a, p);
+    }
     B200Q_CHECK_LAUNCH("qlinear_prefill_kn_kernel");
     return B200Q_OK;
 }
 
 int launch_prefill_kn(const void *a, const void *wq, const void *scale, void *c, int64_t M, int64_t N, int64_t K,
-                      cudaStream_t stream, const OutTargets *targets) {
+                      cudaStream_t stream, const OutTargets *targets, const Epilogue *epilogue) {
     int sms = sm_count();
     if (sms <= 0) sms = 148;
     switch (choose_tile_m(M, N, sms)) {
-        case 64: return launch_prefill_tm<64>(a, wq, scale, c, M, N, K, stream, targets, sms);
-        default: return launch_prefill_tm<256>(a, wq, scale, c, M, N, K, stream, targets, sms);
+        case 64: return launch_prefill_tm<64>(a, wq, scale, c, M, N, K, stream, targets, epilogue, sms);
+        default: return launch_prefill_tm<256>(a, wq, scale, c, M, N, K, stream, targets, epilogue, sms);
     }
 }
 

@@ -38,6 +38,13 @@ KERNEL_TIMEOUT = 5
 F16, BF16, F32 = 0, 1, 2
 I8, I16 = 0, 1
 LAYOUT_KN, LAYOUT_NK = 0, 1
+ACT_NONE, ACT_SILU_MUL = 0, 1
+
+
+class Epilogue(ctypes.Structure):
+    """b200q_epilogue of include/hidet_b200q.h."""
+
+    _fields_ = [('bias', c_void_p), ('residual', c_void_p), ('ldr', c_int64), ('activation', c_int)]
 
 _lib: Optional[ctypes.CDLL] = None
 _funcs: Dict[str, Callable] = {}
@@ -126,6 +133,11 @@ SIGNATURES = {
     'b200q_qlinear_workspace_bytes': ([c_int64, c_int64, c_int64, c_int], c_size_t, False),
     'b200q_qlinear_f16_i8': (
         [c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64, c_int, c_void_p, c_size_t, c_void_p],
+        c_int,
+        True,
+    ),
+    'b200q_qlinear_f16_i8_fused': (
+        [c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64, c_int, c_void_p, c_void_p, c_size_t, c_void_p],
         c_int,
         True,
     ),

@@ -18,6 +18,7 @@ from .patterns import (
     SymmetricLinearQuantizePatternL,
     SymmetricQuantizeMatmulFused,
     SymmetricEmbeddingQuantizePattern,
+    QuantizedLinearEpilogueFusion,
     quantized_matmul,
     quantized_embedding,
     dequantized_weight,

@@ -14,7 +14,7 @@ which gives the same codes and scales as quantizing W[N, K] over dims=1, and the
 from __future__ import annotations
 
 import operator
-from typing import Dict, List, Union
+from typing import Dict, List, Optional, Union
 
 import torch
 import torch.fx as fx
@@ -25,9 +25,24 @@ from .operators import SymmetricDeQuantizationOp, SymmetricQuantizedMatmulOp
 from .transforms import SubgraphRewriteRule
 
 
-def quantized_matmul(a: torch.Tensor, wq: torch.Tensor, scale: torch.Tensor) -> torch.Tensor:
-    """The call the rewritten graph makes: the quantized matmul operator, resolved to the library kernel."""
-    return SymmetricQuantizedMatmulOp(a, wq, scale).outputs[0]
+def _fusable(k: int, n: int) -> bool:
+    """The kernels with a fused epilogue take rows that are multiples of 16 bytes."""
+    return n % 16 == 0 and k % 8 == 0
+
+
+def quantized_matmul(a: torch.Tensor, wq: torch.Tensor, scale: torch.Tensor, bias: Optional[torch.Tensor] = None,
+                     residual: Optional[torch.Tensor] = None, activation: Optional[str] = None) -> torch.Tensor:
+    """The call the rewritten graph makes: the quantized matmul operator, resolved to the library kernel.
+    With bias / residual / activation (folded in by QuantizedLinearEpilogueFusion) the kernel applies them
+    itself; a residual that only broadcasts to the result is added afterwards."""
+    if bias is None and residual is None and activation is None:
+        return SymmetricQuantizedMatmulOp(a, wq, scale).outputs[0]
+    n_out = wq.shape[1] // 2 if activation == 'silu_mul' else wq.shape[1]
+    late = None
+    if residual is not None and (list(residual.shape) != list(a.shape[:-1]) + [n_out] or residual.dtype != torch.float16):
+        late, residual = residual, None
+    out = quant.symmetric_quant_matmul(a, wq, scale, bias=bias, residual=residual, activation=activation)
+    return out if late is None else out + late
 
 
 _MATMULS = {torch.matmul, operator.matmul, torch.mm}
@@ -71,11 +86,16 @@ class SymmetricLinearQuantizePattern(SubgraphRewriteRule):
                     continue
                 wq_node, scale_node = self._install(gm, node, mod.weight.detach().t(), existing + count)
                 with gm.graph.inserting_before(node):
-                    new = gm.graph.call_function(quantized_matmul, (node.args[0], wq_node, scale_node))
                     if mod.bias is not None:
                         bias_name = '_b200q_bias_{}'.format(existing + count)
                         gm.register_buffer(bias_name, mod.bias.detach())
-                        new = gm.graph.call_function(torch.add, (new, gm.graph.get_attr(bias_name)))
+                        bias_node = gm.graph.get_attr(bias_name)
+                        if _fusable(mod.weight.shape[1], mod.weight.shape[0]) and mod.bias.dtype == torch.float16:
+                            new = gm.graph.call_function(quantized_matmul, (node.args[0], wq_node, scale_node), {'bias': bias_node})
+                        else:
+                            new = gm.graph.call_function(torch.add, (gm.graph.call_function(quantized_matmul, (node.args[0], wq_node, scale_node)), bias_node))
+                    else:
+                        new = gm.graph.call_function(quantized_matmul, (node.args[0], wq_node, scale_node))
                 node.replace_all_uses_with(new)
                 gm.graph.erase_node(node)
                 count += 1
@@ -105,9 +125,13 @@ class SymmetricLinearQuantizePattern(SubgraphRewriteRule):
                     continue
                 wq_node, scale_node = self._install(gm, node, w_nk.t(), existing + count)
                 with gm.graph.inserting_before(node):
-                    new = gm.graph.call_function(quantized_matmul, (x, wq_node, scale_node))
-                    if bias is not None:
-                        new = gm.graph.call_function(torch.add, (new, bias))
+                    bias_const = constants.get(bias.name) if isinstance(bias, fx.Node) else None
+                    if bias is not None and bias_const is not None and bias_const.dtype == torch.float16 and _fusable(w_nk.shape[1], w_nk.shape[0]):
+                        new = gm.graph.call_function(quantized_matmul, (x, wq_node, scale_node), {'bias': bias})
+                    else:
+                        new = gm.graph.call_function(quantized_matmul, (x, wq_node, scale_node))
+                        if bias is not None:
+                            new = gm.graph.call_function(torch.add, (new, bias))
                 node.replace_all_uses_with(new)
                 gm.graph.erase_node(node)
                 count += 1
@@ -191,6 +215,91 @@ class SymmetricQuantizeMatmulFused(SubgraphRewriteRule):
         return count
 
 
+_SILUS = {F.silu, torch.nn.functional.silu}
+_MULS = {operator.mul, torch.mul}
+_ADDS = {operator.add, torch.add}
+
+
+class QuantizedLinearEpilogueFusion(SubgraphRewriteRule):
+    """Folds what follows a quantized linear into its kernel:
+        silu(qmm(x, Wg)) * qmm(x, Wu)   =>  qmm(x, interleave(Wg, Wu), activation='silu_mul')   (SwiGLU; one launch, one pass over x)
+        r + qmm(x, W)                   =>  qmm(x, W, residual=r)
+    The reference gets there by fusing element-wise operators into the matmul task as prologues / epilogues
+    (python/hidet/graph/transforms/fuse_operator.py, python/hidet/graph/ops/quant/matmul_f16_i8.py:95-99)."""
+
+    def __init__(self):
+        super().__init__('quantized_linear_epilogue_fusion')
+
+    @staticmethod
+    def _plain_qmm(node) -> bool:
+        return isinstance(node, fx.Node) and node.op == 'call_function' and node.target is quantized_matmul and not node.kwargs and len(node.args) == 3
+
+    def _is_silu(self, gm: fx.GraphModule, node) -> bool:
+        if not isinstance(node, fx.Node):
+            return False
+        if node.op == 'call_function' and node.target in _SILUS:
+            return len(node.args) == 1 and not node.kwargs.get('inplace', False)
+        return node.op == 'call_module' and isinstance(gm.get_submodule(node.target), torch.nn.SiLU)
+
+    def apply(self, gm: fx.GraphModule, constants: Dict[str, torch.Tensor]) -> int:
+        count = 0
+        buffers = dict(gm.named_buffers())
+
+        def const_of(node):
+            return buffers.get(node.target) if isinstance(node, fx.Node) and node.op == 'get_attr' else None
+
+        existing = sum(1 for name in buffers if name.startswith('_b200q_gu_wq_'))
+        for node in list(gm.graph.nodes):
+            if node.op != 'call_function' or node.target not in _MULS or len(node.args) != 2:
+                continue
+            for act, up in (node.args, node.args[::-1]):
+                if not (self._is_silu(gm, act) and self._plain_qmm(act.args[0]) and self._plain_qmm(up)):
+                    continue
+                gate = act.args[0]
+                if gate.args[0] is not up.args[0] or len(gate.users) != 1 or len(act.users) != 1 or len(up.users) != 1:
+                    continue
+                wq_g, s_g, wq_u, s_u = (const_of(n) for n in (gate.args[1], gate.args[2], up.args[1], up.args[2]))
+                if any(t is None for t in (wq_g, s_g, wq_u, s_u)) or wq_g.shape != wq_u.shape or not _fusable(wq_g.shape[0], 2 * wq_g.shape[1]):
+                    continue
+                wq_name, scale_name = '_b200q_gu_wq_{}'.format(existing + count), '_b200q_gu_scale_{}'.format(existing + count)
+                gm.register_buffer(wq_name, quant.interleave_gate_up(wq_g, wq_u))
+                gm.register_buffer(scale_name, quant.interleave_gate_up(s_g, s_u))
+                with gm.graph.inserting_before(node):
+                    new = gm.graph.call_function(quantized_matmul, (gate.args[0], gm.graph.get_attr(wq_name), gm.graph.get_attr(scale_name)),
+                                                 {'activation': 'silu_mul'})
+                node.replace_all_uses_with(new)
+                for dead in (node, act, gate, up):
+                    gm.graph.erase_node(dead)
+                count += 1
+                break
+        for node in list(gm.graph.nodes):
+            if node.op != 'call_function' or node.target not in _ADDS or len(node.args) != 2 or node.kwargs:
+                continue
+            for q, r in (node.args, node.args[::-1]):
+                if not (isinstance(q, fx.Node) and q.op == 'call_function' and q.target is quantized_matmul and 'residual' not in q.kwargs):
+                    continue
+                if len(q.users) != 1 or not isinstance(r, fx.Node) or r is q:
+                    continue
+                wq = const_of(q.args[1])
+                if wq is None or not _fusable(wq.shape[0], wq.shape[1]):
+                    continue
+                with gm.graph.inserting_before(node):
+                    new = gm.graph.call_function(quantized_matmul, q.args, dict(q.kwargs, residual=r))
+                node.replace_all_uses_with(new)
+                gm.graph.erase_node(node)
+                gm.graph.erase_node(q)
+                count += 1
+                break
+        # weights that only the unfused calls used
+        if count:
+            gm.graph.eliminate_dead_code()
+            used = {n.target for n in gm.graph.nodes if n.op == 'get_attr'}
+            for name in list(buffers):
+                if name.startswith('_b200q_') and name not in used and hasattr(gm, name):
+                    delattr(gm, name)
+        return count
+
+
 def quantized_embedding(indices: torch.Tensor, wq: torch.Tensor, scale: torch.Tensor) -> torch.Tensor:
     """The call the rewritten graph makes for an embedding: lookup in the row-quantized table."""
     return quant.symmetric_dequantize_take(wq, scale, indices)
@@ -252,5 +361,7 @@ def symmetric_embedding_quantize_patterns(quant_type: str = 'int8') -> List[Subg
 
 
 def default_patterns() -> List[SubgraphRewriteRule]:
-    """python/hidet/graph/transforms/graph_patterns/quant/__init__.py:19-28: embedding tables and linear layers."""
-    return symmetric_embedding_quantize_patterns(quant_type='int8') + symmetric_linear_patterns(quant_type='int8', dims=0)
+    """python/hidet/graph/transforms/graph_patterns/quant/__init__.py:19-28: embedding tables and linear layers; then
+    the fusion of what follows a quantized linear into its kernel (in the reference a later pass, fuse_operator)."""
+    return (symmetric_embedding_quantize_patterns(quant_type='int8') + symmetric_linear_patterns(quant_type='int8', dims=0) +
+            [QuantizedLinearEpilogueFusion()])

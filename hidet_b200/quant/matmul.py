@@ -7,6 +7,7 @@ and error messages; the kernels are those of libhidet_b200q.so.
 """
 from __future__ import annotations
 
+import ctypes
 from typing import Optional
 
 import torch
@@ -48,8 +49,21 @@ def _check_operands(a: torch.Tensor, weight: torch.Tensor, scale: torch.Tensor, 
     return m, n, k_w
 
 
+_ACTIVATIONS = {None: ffi.ACT_NONE, 'none': ffi.ACT_NONE, 'silu_mul': ffi.ACT_SILU_MUL}
+
+
+def interleave_gate_up(gate: torch.Tensor, up: torch.Tensor) -> torch.Tensor:
+    """Two tensors of equal shape [..., F] -> [..., 2F] with gate[..., j] at column 2j and up[..., j] at 2j + 1:
+    the column order activation='silu_mul' expects.  Works for the float weights before quantization, for
+    int8 codes and for scales alike (quantization is per column, so it commutes with the interleaving)."""
+    if gate.shape != up.shape or gate.dtype != up.dtype:
+        raise ValueError('gate and up must have equal shapes and dtypes, got {} {} and {} {}'.format(list(gate.shape), gate.dtype, list(up.shape), up.dtype))
+    return torch.stack((gate, up), dim=-1).reshape(*gate.shape[:-1], 2 * gate.shape[-1]).contiguous()
+
+
 def symmetric_quant_matmul(a: torch.Tensor, weight: torch.Tensor, scale: torch.Tensor, weight_layout: str = 'KN',
-                           out: Optional[torch.Tensor] = None) -> torch.Tensor:
+                           out: Optional[torch.Tensor] = None, bias: Optional[torch.Tensor] = None,
+                           residual: Optional[torch.Tensor] = None, activation: Optional[str] = None) -> torch.Tensor:
     """c[..., M, N] = a[..., M, K] @ (float16(weight) * scale), accumulated in fp32, rounded to f16 once.
 
     weight is int8 [K, N] with scale [N] (weight_layout='KN', the reference's contract,
@@ -57,12 +71,35 @@ def symmetric_quant_matmul(a: torch.Tensor, weight: torch.Tensor, scale: torch.T
     torch.nn.Linear keeps; not offered by the reference).  `out`, if given, receives the result (a
     contiguous float16 CUDA tensor of the output shape), so that a caller replaying a fixed sequence
     of calls allocates nothing.
+
+    bias [N], activation and residual are applied inside the kernel to the fp32 sums, in that order, and the
+    result is rounded to f16 once -- what the reference gets by fusing the following element-wise operators
+    into the matmul (python/hidet/graph/transforms/fuse_operator.py).  activation='silu_mul': the weight's
+    columns are (gate_j, up_j) pairs (see interleave_gate_up) and the result, N / 2 wide, is
+    silu(gate) * up.  residual has the shape of the result.
     """
     m, n, k = _check_operands(a, weight, scale, weight_layout)
+    if activation not in _ACTIVATIONS:
+        raise ValueError("activation must be None or 'silu_mul', got {!r}".format(activation))
+    fused = bias is not None or residual is not None or _ACTIVATIONS[activation] != ffi.ACT_NONE
+    n_out = n // 2 if _ACTIVATIONS[activation] == ffi.ACT_SILU_MUL else n
     a2 = a.contiguous()
     weight = weight.contiguous()
     scale = scale.contiguous()
-    out_shape = list(a.shape[:-1]) + [n]
+    out_shape = list(a.shape[:-1]) + [n_out]
+    if fused:
+        if weight_layout != 'KN':
+            raise ValueError("bias, residual and activation are fused for weight_layout='KN' only")
+        if bias is not None:
+            require_cuda(bias, 'bias')
+            if bias.dtype != torch.float16 or list(bias.shape) != [n]:
+                raise ValueError('Expect a float16 bias of shape [{}], got {} {}'.format(n, bias.dtype, list(bias.shape)))
+            bias = bias.contiguous()
+        if residual is not None:
+            require_cuda(residual, 'residual')
+            if residual.dtype != torch.float16 or list(residual.shape) != out_shape:
+                raise ValueError('Expect a float16 residual of shape {}, got {} {}'.format(out_shape, residual.dtype, list(residual.shape)))
+            residual = residual.contiguous()
     if out is None:
         c = torch.empty(out_shape, dtype=torch.float16, device=a.device)
     else:
@@ -73,10 +110,18 @@ def symmetric_quant_matmul(a: torch.Tensor, weight: torch.Tensor, scale: torch.T
     with torch.cuda.device(a.device):
         ws_bytes = ffi.func('b200q_qlinear_workspace_bytes')(m, n, k, layout)
         ws_ptr, ws_size = workspaces.get(a.device, ws_bytes)
-        ffi.func('b200q_qlinear_f16_i8')(
-            a2.data_ptr(), weight.data_ptr(), scale.data_ptr(), c.data_ptr(), m, n, k, layout, ws_ptr, ws_size,
-            current_stream_ptr(a.device),
-        )
+        if fused:
+            ep = ffi.Epilogue(bias.data_ptr() if bias is not None else None, residual.data_ptr() if residual is not None else None,
+                              n_out, _ACTIVATIONS[activation])
+            ffi.func('b200q_qlinear_f16_i8_fused')(
+                a2.data_ptr(), weight.data_ptr(), scale.data_ptr(), c.data_ptr(), m, n, k, layout, ctypes.byref(ep), ws_ptr, ws_size,
+                current_stream_ptr(a.device),
+            )
+        else:
+            ffi.func('b200q_qlinear_f16_i8')(
+                a2.data_ptr(), weight.data_ptr(), scale.data_ptr(), c.data_ptr(), m, n, k, layout, ws_ptr, ws_size,
+                current_stream_ptr(a.device),
+            )
     return c
 
 

@@ -137,6 +137,35 @@ B200Q_API int b200q_qlinear_f16_i8(const void *a, const void *wq, const void *sc
                                    int64_t K, int w_layout, void *workspace, size_t workspace_bytes, void *stream);
 
 /*
+ * What b200q_qlinear_f16_i8_fused does to the scaled fp32 sums y[m, n] before the one rounding to f16, in
+ * this order:  y += bias[n];  the activation;  + residual[m, .].
+ * B200Q_ACT_SILU_MUL is the SwiGLU pairing: the N columns of the weight come in pairs (gate_j, up_j) at
+ * (2j, 2j + 1) -- a gate and an up projection [K, F] each, interleaved column by column into one [K, 2F]
+ * weight (quantization is per column, so codes and scales are those of the two separate weights) -- and
+ * the result is z[m, j] = silu(y[m, 2j]) * y[m, 2j + 1], N / 2 columns wide.
+ */
+typedef enum b200q_activation { B200Q_ACT_NONE = 0, B200Q_ACT_SILU_MUL = 1 } b200q_activation;
+typedef struct b200q_epilogue {
+    const void *bias;     /* f16 [N], or NULL                                                     */
+    const void *residual; /* f16 [M, ldr], added to the result (after the activation), or NULL    */
+    int64_t ldr;          /* elements between rows of residual; at least the width of the result  */
+    int activation;       /* b200q_activation                                                     */
+} b200q_epilogue;
+
+/*
+ * b200q_qlinear_f16_i8 with the element-wise operators that follow a linear layer applied inside the
+ * kernel: c[M, N or N / 2] = epilogue(a x dequant(wq, scale)).  Takes the place of the reference's fusion of
+ * those operators into its matmul by IR rewriting (python/hidet/graph/transforms/fuse_operator.py,
+ * python/hidet/graph/ops/quant/matmul_f16_i8.py:95-99: the task allows an epilogue); the intermediate
+ * values stay in fp32, so the result is rounded once where the unfused graph rounds after every operator.
+ * [K, N] weights with 16-byte aligned bases and rows; workspace as for b200q_qlinear_f16_i8 with the same
+ * M, N, K.  epilogue == NULL is b200q_qlinear_f16_i8.
+ */
+B200Q_API int b200q_qlinear_f16_i8_fused(const void *a, const void *wq, const void *scale, void *c, int64_t M, int64_t N,
+                                         int64_t K, int w_layout, const b200q_epilogue *epilogue, void *workspace,
+                                         size_t workspace_bytes, void *stream);
+
+/*
  * The reference's explicit split-K form: c[p, M, N] (f16) = scale[n] * sum over the p-th K part of
  * a[m, k] * wq[k, n], parts of ceil(K / k_parts) consecutive k (the last may be short or empty).
  * The caller sums over p.  Replaces symmetric_quant_matmul_f16_i8

@@ -88,8 +88,8 @@ def test_quantization_pass_rewrites_matmul_and_linear():
     assert torch.allclose(got.float(), want.float(), atol=2e-1, rtol=2e-1)
     # and exactly what the ops give when called by hand
     h = F.silu(hidet_b200.symmetric_quant_matmul(x, buffers['_b200q_wq_0'], buffers['_b200q_scale_0']))
-    manual = hidet_b200.symmetric_quant_matmul(h, buffers['_b200q_wq_1'], buffers['_b200q_scale_1']) + model.fc.bias
-    assert torch.equal(got, manual)
+    manual = hidet_b200.symmetric_quant_matmul(h, buffers['_b200q_wq_1'], buffers['_b200q_scale_1'], bias=model.fc.bias.detach())
+    assert torch.equal(got, manual)   # the bias is added inside the kernel
 
 
 class LeftConstant(nn.Module):
@@ -187,6 +187,37 @@ class Block(nn.Module):
         x = x + self.o(a)
         y = self.rms(x, self.n2)
         return x + self.down(F.silu(self.gate(y)) * self.up(y))
+
+
+def test_epilogue_fusion_folds_swiglu_and_residuals_into_the_kernels():
+    torch.manual_seed(5)
+    model = Block().half().cuda().eval()
+    x = torch.randn(2, 16, 256, device='cuda').half()
+    with torch.no_grad():
+        want = model(x)
+    gm = fx.symbolic_trace(model)
+    with hg.PassContext() as ctx:
+        ctx.set_precision('int8')
+        hg.optimize(gm)
+    calls = [n for n in gm.graph.nodes if n.op == 'call_function' and n.target is hg.quantized_matmul]
+    kinds = sorted((tuple(sorted(n.kwargs)) for n in calls))
+    # q, k, v plain; o and down with the residual; gate and up as one launch with the SwiGLU pairing
+    assert kinds == [(), (), (), ('activation',), ('residual',), ('residual',)]
+    buffers = dict(gm.named_buffers())
+    assert tuple(buffers['_b200q_gu_wq_0'].shape) == (256, 2 * 688)
+    assert sum(1 for name in buffers if name.startswith('_b200q_wq_')) == 5   # the separate gate and up weights are gone
+    with torch.no_grad():
+        got = gm(x)
+    assert (got.float() - want.float()).abs().max() < 5e-2
+    # unfused rewrite of the same model: same result up to the float16 roundings the fusion removes
+    gm2 = fx.symbolic_trace(model)
+    with hg.PassContext() as ctx:
+        ctx.add_quantize_rules(hg.symmetric_linear_patterns('int8', 0))
+        hg.optimize(gm2)
+    with torch.no_grad():
+        unfused = gm2(x)
+    assert sum(1 for n in gm2.graph.nodes if n.op == 'call_function' and n.target is hg.quantized_matmul) == 7
+    assert (got.float() - unfused.float()).abs().max() < 2e-2
 
 
 def test_torch_compile_backend_quantizes_a_decoder_block():
