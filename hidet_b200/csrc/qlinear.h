@@ -53,12 +53,16 @@ bool decode_kn_supported(const void *a, const void *wq, int64_t N, int64_t K);
 // c[M, N] = scale * (a[:, k_begin:k_end] x wq[k_begin:k_end, :]).  K is the row length of `a`.
 int launch_decode_kn(const void *a, const void *wq, const void *scale, void *c, int64_t M, int64_t N, int64_t K,
                      int64_t k_begin, int64_t k_end, bool allow_split, void *workspace, size_t workspace_bytes,
-                     cudaStream_t stream, const OutTargets *targets = nullptr, const Epilogue *epilogue = nullptr);
+                     cudaStream_t stream, const OutTargets *targets = nullptr, const Epilogue *epilogue = nullptr, bool weight_nk = false);
+// The same kernel on a weight stored [N, K] (weight_nk = true): needs 16-byte aligned bases and K % 16 == 0.
+bool decode_nk_supported(const void *a, const void *wq, int64_t N, int64_t K);
 
 // The tensor-memory kernel for large M: same operand requirements as the small-M kernel.
 bool prefill_kn_supported(const void *a, const void *wq, int64_t N, int64_t K);
 int launch_prefill_kn(const void *a, const void *wq, const void *scale, void *c, int64_t M, int64_t N, int64_t K,
-                      cudaStream_t stream, const OutTargets *targets = nullptr, const Epilogue *epilogue = nullptr);
+                      cudaStream_t stream, const OutTargets *targets = nullptr, const Epilogue *epilogue = nullptr, bool weight_nk = false);
+// The same kernel on a weight stored [N, K] (weight_nk = true): 16-byte aligned bases, K % 16 == 0, N % 8 == 0.
+bool prefill_nk_supported(const void *a, const void *wq, int64_t N, int64_t K);
 
 // Which kernel serves M activation rows.  The tensor-memory kernel's tiles span 64 or 256 rows and it
 // streams every weight tile once per row block; the small-M kernel re-streams the weight once per 16

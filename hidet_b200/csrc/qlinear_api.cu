@@ -79,8 +79,14 @@ B200Q_API int b200q_qlinear_f16_i8(const void *a, const void *wq, const void *sc
     if (w_layout == B200Q_LAYOUT_KN && use_prefill_kernel(M, N, K) && prefill_kn_supported(a, wq, N, K)) {
         return launch_prefill_kn(a, wq, scale, c, M, N, K, s);
     }
+    if (w_layout == B200Q_LAYOUT_NK && use_prefill_kernel(M, N, K) && prefill_nk_supported(a, wq, N, K)) {
+        return launch_prefill_kn(a, wq, scale, c, M, N, K, s, nullptr, nullptr, true);
+    }
     if (w_layout == B200Q_LAYOUT_KN && decode_kn_supported(a, wq, N, K)) {
         return launch_decode_kn(a, wq, scale, c, M, N, K, 0, K, true, workspace, workspace_bytes, s);
+    }
+    if (w_layout == B200Q_LAYOUT_NK && decode_nk_supported(a, wq, N, K)) {
+        return launch_decode_kn(a, wq, scale, c, M, N, K, 0, K, true, workspace, workspace_bytes, s, nullptr, nullptr, true);
     }
     return launch_generic(a, wq, scale, c, M, N, K, 0, K, w_layout, s);
 }

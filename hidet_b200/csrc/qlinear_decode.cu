@@ -77,6 +77,15 @@ __device__ __forceinline__ void cvt_s8x4_to_f16_pairs(uint32_t v, uint32_t &p01,
     asm("sub.f16x2 %0, %1, %2;" : "=r"(p23) : "r"(e23), "r"(bias));
 }
 
+// Four 8 x 16 byte tiles as they lie.  Lanes 8i .. 8i+7 give the addresses of the rows of tile i; lane
+// (g = lane / 4, t = lane % 4) receives in r[i] the bytes 4t .. 4t+3 of row g of tile i.  With a weight
+// stored as [column][k] that is again four consecutive k of one column per register.
+__device__ __forceinline__ void ldmatrix_x4_b16(uint32_t (&r)[4], uint32_t addr) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0, %1, %2, %3}, [%4];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
+                 : "r"(addr));
+}
+
 // D[16 x 8] += A[16 x 16] * B[16 x 8]: A row-major (here: 16 weight columns x 16 k), B column-major
 // (here: 16 k x 8 activation rows).
 __device__ __forceinline__ void mma_m16n8k16(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0,
@@ -185,7 +194,10 @@ struct Params {
 };
 
 // MT: 8-row blocks of activations per CTA (1: up to 8 rows, 2: up to 16).
-template <int MT>
+// NK: the weight is [N, K] with K contiguous (the layout torch.nn.Linear keeps) instead of the reference's
+//     [K, N]: a stage is then 128 weight rows of 64 k-bytes (64-byte swizzle) and the fragments come from
+//     plain matrix loads; everything else is shared.
+template <int MT, bool NK>
 __global__ void __launch_bounds__(THREADS) qlinear_decode_kn_kernel(const __grid_constant__ CUtensorMap map_w,
                                                                     const __grid_constant__ CUtensorMap map_a,
                                                                     const Params p) {
@@ -269,7 +281,7 @@ __global__ void __launch_bounds__(THREADS) qlinear_decode_kn_kernel(const __grid
             for (int it = 0; it < prologue; ++it) {
                 const uint32_t bar = smem_u32(&full_bar[it]);
                 mbar_expect_tx(bar, W_STAGE_BYTES);
-                tma_load_2d_hint(w_base + it * W_STAGE_BYTES, &map_w, n0, p.k_begin + (it_begin + it) * BK, bar, stream_policy);
+                tma_load_2d_hint(w_base + it * W_STAGE_BYTES, &map_w, NK ? p.k_begin + (it_begin + it) * BK : n0, NK ? n0 : p.k_begin + (it_begin + it) * BK, bar, stream_policy);
             }
             pdl_wait();
             for (int it = 0; it < prologue; ++it) {
@@ -286,7 +298,7 @@ __global__ void __launch_bounds__(THREADS) qlinear_decode_kn_kernel(const __grid
                 const uint32_t bar = smem_u32(&full_bar[s]);
                 const int k0 = p.k_begin + (it_begin + it) * BK;
                 mbar_expect_tx(bar, W_STAGE_BYTES);
-                tma_load_2d_hint(w_base + s * W_STAGE_BYTES, &map_w, n0, k0, bar, stream_policy);
+                tma_load_2d_hint(w_base + s * W_STAGE_BYTES, &map_w, NK ? k0 : n0, NK ? n0 : k0, bar, stream_policy);
                 mbar_expect_tx(bar, A_STAGE_BYTES);
                 tma_load_2d(a_base + s * A_STAGE_BYTES, &map_a, k0, m0, bar);
             }
@@ -300,6 +312,10 @@ __global__ void __launch_bounds__(THREADS) qlinear_decode_kn_kernel(const __grid
         // chunks 2 warp and 2 warp + 1 of each row).  Lane l addresses row (l & 15) of chunk
         // 2 warp + (l >> 4); under the 128B swizzle chunk c of row r sits at chunk c ^ (r & 7).
         const uint32_t off_w = (lane & 15) * 128 + (((2 * warp + (lane >> 4)) ^ (lane & 7)) << 4);
+        // [N, K] weights: lane l addresses row 32 warp + 8 (l / 8 % 2) + l % 8 (+ 16 j) of the stage, 16-byte
+        // chunk l / 16 (+ 2 per 32 k); rows are 64 bytes, chunk c of row r sits at chunk c ^ (r / 2 % 4).
+        const uint32_t nk_row = 32 * warp + 8 * ((lane >> 3) & 1) + (lane & 7);
+        const uint32_t nk_chunk = (uint32_t)lane >> 4;
         // Activations: row g (and g + 8, same swizzle phase), k = 16 ks + 4t .. 4t+3: bytes 8 (t & 1) of
         // chunk 2 ks + (t >> 1).
         const uint32_t off_a = g * 128 + 8 * (t & 1);
@@ -316,9 +332,23 @@ __global__ void __launch_bounds__(THREADS) qlinear_decode_kn_kernel(const __grid
             uint2 b[4][MT];
 #pragma unroll
             for (int ks = 0; ks < 4; ++ks) {
-                ldmatrix_x2_trans_b8(q[ks], wb + ks * 2048);
+                if (!NK) ldmatrix_x2_trans_b8(q[ks], wb + ks * 2048);
 #pragma unroll
                 for (int mt = 0; mt < MT; ++mt) b[ks][mt] = lds64(ab + mt * 1024 + (((2 * ks) ^ a_chunk) << 4));
+            }
+            if (NK) {
+#pragma unroll
+                for (int j = 0; j < 2; ++j)
+#pragma unroll
+                    for (int kh = 0; kh < 2; ++kh) {
+                        const uint32_t row = nk_row + 16 * j;
+                        uint32_t r[4];
+                        ldmatrix_x4_b16(r, w_base + s * W_STAGE_BYTES + row * 64 + (((2 * kh + nk_chunk) ^ ((row >> 1) & 3)) << 4));
+                        q[2 * kh][2 * j] = r[0];
+                        q[2 * kh][2 * j + 1] = r[1];
+                        q[2 * kh + 1][2 * j] = r[2];
+                        q[2 * kh + 1][2 * j + 1] = r[3];
+                    }
             }
             __syncwarp();
             if (lane == 0) mbar_arrive(smem_u32(&empty_bar[s]));  // the stage is in registers now
@@ -520,9 +550,14 @@ bool decode_kn_supported(const void *a, const void *wq, int64_t N, int64_t K) {
            ((reinterpret_cast<uintptr_t>(wq) & 15u) == 0);
 }
 
+bool decode_nk_supported(const void *a, const void *wq, int64_t N, int64_t K) {
+    (void)N;
+    return (K % 16 == 0) && ((reinterpret_cast<uintptr_t>(a) & 15u) == 0) && ((reinterpret_cast<uintptr_t>(wq) & 15u) == 0);
+}
+
 int launch_decode_kn(const void *a, const void *wq, const void *scale, void *c, int64_t M, int64_t N, int64_t K,
                      int64_t k_begin, int64_t k_end, bool allow_split, void *workspace, size_t workspace_bytes,
-                     cudaStream_t stream, const OutTargets *targets, const Epilogue *epilogue) {
+                     cudaStream_t stream, const OutTargets *targets, const Epilogue *epilogue, bool weight_nk) {
     using namespace decode;
     DecodePlan pl = plan_decode(M, N, k_end - k_begin);
     if (!allow_split) {
@@ -540,8 +575,10 @@ int launch_decode_kn(const void *a, const void *wq, const void *scale, void *c, 
     if (pl.m_tiles > 65535 || pl.splits > 65535) return set_error(B200Q_UNSUPPORTED, "qlinear: M=%lld is too large for the small-M kernel", (long long)M);
 
     CUtensorMap map_w, map_a;
-    int rc = make_tensor_map_2d(&map_w, CU_TENSOR_MAP_DATA_TYPE_UINT8, wq, (uint64_t)N, (uint64_t)k_end, (uint64_t)N, BN, BK,
-                                CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B);
+    int rc = weight_nk ? make_tensor_map_2d(&map_w, CU_TENSOR_MAP_DATA_TYPE_UINT8, wq, (uint64_t)k_end, (uint64_t)N, (uint64_t)K, BK, BN,
+                                            CU_TENSOR_MAP_SWIZZLE_64B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B)
+                       : make_tensor_map_2d(&map_w, CU_TENSOR_MAP_DATA_TYPE_UINT8, wq, (uint64_t)N, (uint64_t)k_end, (uint64_t)N, BN, BK,
+                                            CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B);
     if (rc != B200Q_OK) return rc;
     rc = make_tensor_map_2d(&map_a, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, a, (uint64_t)k_end, (uint64_t)M, (uint64_t)K * 2, BK, BM,
                             CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B);
@@ -570,15 +607,19 @@ int launch_decode_kn(const void *a, const void *wq, const void *scale, void *c, 
     p.cols_per = (int)round_up(ceil_div(BN, pl.cluster), 8);
     p.mode = pl.splits == 1 ? kModeDirect : kModeSplit;
 
-    auto kernel = (M - (int64_t)(pl.m_tiles - 1) * BM <= 8 && pl.m_tiles == 1) ? qlinear_decode_kn_kernel<1> : qlinear_decode_kn_kernel<2>;
+    const bool one_block = M - (int64_t)(pl.m_tiles - 1) * BM <= 8 && pl.m_tiles == 1;
+    auto kernel = weight_nk ? (one_block ? qlinear_decode_kn_kernel<1, true> : qlinear_decode_kn_kernel<2, true>)
+                            : (one_block ? qlinear_decode_kn_kernel<1, false> : qlinear_decode_kn_kernel<2, false>);
     static bool attr_set[64] = {false};  // per device; a repeated set is harmless
     int dev = 0;
     B200Q_CUDA_TRY(cudaGetDevice(&dev));
     if (dev < 0 || dev >= 64 || !attr_set[dev]) {
-        B200Q_CUDA_TRY(cudaFuncSetAttribute(qlinear_decode_kn_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
-        B200Q_CUDA_TRY(cudaFuncSetAttribute(qlinear_decode_kn_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
-        B200Q_CUDA_TRY(cudaFuncSetAttribute(qlinear_decode_kn_kernel<1>, cudaFuncAttributeNonPortableClusterSizeAllowed, 1));
-        B200Q_CUDA_TRY(cudaFuncSetAttribute(qlinear_decode_kn_kernel<2>, cudaFuncAttributeNonPortableClusterSizeAllowed, 1));
+        const void *all[4] = {reinterpret_cast<const void *>(qlinear_decode_kn_kernel<1, false>), reinterpret_cast<const void *>(qlinear_decode_kn_kernel<2, false>),
+                              reinterpret_cast<const void *>(qlinear_decode_kn_kernel<1, true>), reinterpret_cast<const void *>(qlinear_decode_kn_kernel<2, true>)};
+        for (const void *f : all) {
+            B200Q_CUDA_TRY(cudaFuncSetAttribute(f, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
+            B200Q_CUDA_TRY(cudaFuncSetAttribute(f, cudaFuncAttributeNonPortableClusterSizeAllowed, 1));
+        }
         if (dev >= 0 && dev < 64) attr_set[dev] = true;
     }
     cudaLaunchConfig_t cfg = {};

@@ -63,6 +63,8 @@ struct Config {
     // tcgen05 instruction descriptor, kind::f16: D = f32, A = B = f16, A is MN-major, B is K-major,
     // N = TM (bits 17..22 hold N / 8), M = 128 (bits 24..28 hold M / 16).
     static constexpr uint32_t kInstrDesc = (1u << 4) | (1u << 15) | ((uint32_t)(TM >> 3) << 17) | ((uint32_t)(TN >> 4) << 24);
+    // the same with A K-major (bit 15 clear): a weight stored [N, K] is converted row by row
+    static constexpr uint32_t kInstrDescNK = (1u << 4) | ((uint32_t)(TM >> 3) << 17) | ((uint32_t)(TN >> 4) << 24);
 };
 
 // Shared-memory matrix descriptor: start address, leading / stride byte offsets (all in 16-byte
@@ -143,7 +145,9 @@ struct Params {
 };
 
 // FUSED: the epilogue of p.ep (bias, gate / up pairing, residual) is compiled in.
-template <int TM, bool FUSED>
+// NK: the weight is [N, K] with K contiguous: the int8 tile is 128 weight rows of 64 k-bytes and its f16
+//     image is the K-major MMA operand (rows of 128 bytes, 128B swizzle), like the activation tile.
+template <int TM, bool FUSED, bool NK>
 __global__ void __launch_bounds__(THREADS, 1) qlinear_prefill_kn_kernel(const __grid_constant__ CUtensorMap map_w,
                                                                         const __grid_constant__ CUtensorMap map_a,
                                                                         const Params p) {
@@ -223,7 +227,7 @@ __global__ void __launch_bounds__(THREADS, 1) qlinear_prefill_kn_kernel(const __
                     }
                     const uint32_t raw_bar = smem_u32(&raw_full[r][i % CONV_GROUPS]);  // the group that converts stage i
                     mbar_expect_tx(raw_bar, RAW_BYTES);
-                    tma_load_2d_hint(raw_addr(r), &map_w, n0, kb * BK, raw_bar, keep);
+                    tma_load_2d_hint(raw_addr(r), &map_w, NK ? kb * BK : n0, NK ? n0 : kb * BK, raw_bar, keep);
                     const int s = i % STAGES;
                     const uint32_t use = i / STAGES;
                     if (use >= 1 && !mbar_wait(smem_u32(&slot_free[s]), (use - 1) & 1)) {
@@ -261,10 +265,11 @@ __global__ void __launch_bounds__(THREADS, 1) qlinear_prefill_kn_kernel(const __
 #pragma unroll
                     for (int ks = 0; ks < BK / 16; ++ks) {
                         // A: MN-major f16 weights, column blocks 8192 B apart, 8-k groups 1024 B apart; K = 16 is two groups.
-                        const uint64_t da = smem_desc(wf_addr(s) + ks * 2048, 8192, 1024);
+                        // ([N, K] weights: K-major like B.)
+                        const uint64_t da = NK ? smem_desc(wf_addr(s) + ks * 32, 16, 1024) : smem_desc(wf_addr(s) + ks * 2048, 8192, 1024);
                         // B: K-major activations, 8-row groups 1024 B apart; K = 16 is 32 bytes along the swizzled row.
                         const uint64_t db = smem_desc(act_addr(s) + ks * 32, 16, 1024);
-                        umma_f16(d_addr, da, db, Cfg::kInstrDesc, (kb > 0 || ks > 0) ? 1u : 0u);
+                        umma_f16(d_addr, da, db, NK ? Cfg::kInstrDescNK : Cfg::kInstrDesc, (kb > 0 || ks > 0) ? 1u : 0u);
                     }
                     umma_commit(smem_u32(&slot_free[s]));
                 }
@@ -303,9 +308,26 @@ __global__ void __launch_bounds__(THREADS, 1) qlinear_prefill_kn_kernel(const __
                 const uint32_t raw = raw_addr(r), wf = wf_addr(s);
                 uint4 v[BK / CONV_ROWS];
 #pragma unroll
-                for (int pass = 0; pass < BK / CONV_ROWS; ++pass) v[pass] = lds128(raw + (pass * CONV_ROWS + rb) * 128 + ci * 16);
+                for (int pass = 0; pass < BK / CONV_ROWS; ++pass)
+                    v[pass] = NK ? lds128(raw + (pass * (32 * GROUP_WARPS) + ct) * 16) : lds128(raw + (pass * CONV_ROWS + rb) * 128 + ci * 16);
                 __syncwarp();
                 if (lane == 0) mbar_arrive(smem_u32(&raw_empty[r]));  // the int8 tile is in registers
+                if (NK) {
+                    // 16-byte piece `id` of the tile is 16 k of weight row id / 4: two 8-k chunks of that row's 128 f16 bytes
+#pragma unroll
+                    for (int pass = 0; pass < BK / CONV_ROWS; ++pass) {
+                        const int id = pass * (32 * GROUP_WARPS) + ct;
+                        const int n = id >> 2, c2 = (id & 3) * 2;
+                        uint32_t h[8];
+                        cvt_s8x4_to_f16_pairs(v[pass].x, h[0], h[1]);
+                        cvt_s8x4_to_f16_pairs(v[pass].y, h[2], h[3]);
+                        cvt_s8x4_to_f16_pairs(v[pass].z, h[4], h[5]);
+                        cvt_s8x4_to_f16_pairs(v[pass].w, h[6], h[7]);
+                        const uint32_t row = wf + n * 128;
+                        sts128(row + ((c2 ^ (n & 7)) << 4), h[0], h[1], h[2], h[3]);
+                        sts128(row + (((c2 + 1) ^ (n & 7)) << 4), h[4], h[5], h[6], h[7]);
+                    }
+                } else
 #pragma unroll
                 for (int pass = 0; pass < BK / CONV_ROWS; ++pass) {
                     const int k = pass * CONV_ROWS + rb;
@@ -437,12 +459,14 @@ static int choose_tile_m(int64_t M, int64_t N, int sms) {
 
 template <int TM>
 static int launch_prefill_tm(const void *a, const void *wq, const void *scale, void *c, int64_t M, int64_t N, int64_t K,
-                             cudaStream_t stream, const OutTargets *targets, const Epilogue *epilogue, int sms) {
+                             cudaStream_t stream, const OutTargets *targets, const Epilogue *epilogue, int sms, bool weight_nk) {
     using namespace prefill;
     using Cfg = Config<TM>;
     CUtensorMap map_w, map_a;
-    int rc = make_tensor_map_2d(&map_w, CU_TENSOR_MAP_DATA_TYPE_UINT8, wq, (uint64_t)N, (uint64_t)K, (uint64_t)N, TN, BK,
-                                CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B);
+    int rc = weight_nk ? make_tensor_map_2d(&map_w, CU_TENSOR_MAP_DATA_TYPE_UINT8, wq, (uint64_t)K, (uint64_t)N, (uint64_t)K, BK, TN,
+                                            CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B)
+                       : make_tensor_map_2d(&map_w, CU_TENSOR_MAP_DATA_TYPE_UINT8, wq, (uint64_t)N, (uint64_t)K, (uint64_t)N, TN, BK,
+                                            CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B);
     if (rc != B200Q_OK) return rc;
     rc = make_tensor_map_2d(&map_a, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, a, (uint64_t)K, (uint64_t)M, (uint64_t)K * 2, BK, TM,
                             CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B);
@@ -477,26 +501,35 @@ static int launch_prefill_tm(const void *a, const void *wq, const void *scale, v
     int dev = 0;
     B200Q_CUDA_TRY(cudaGetDevice(&dev));
     if (dev < 0 || dev >= 64 || !attr_set[dev]) {
-        B200Q_CUDA_TRY(cudaFuncSetAttribute(qlinear_prefill_kn_kernel<TM, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES));
-        B200Q_CUDA_TRY(cudaFuncSetAttribute(qlinear_prefill_kn_kernel<TM, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES));
+        B200Q_CUDA_TRY(cudaFuncSetAttribute(qlinear_prefill_kn_kernel<TM, false, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES));
+        B200Q_CUDA_TRY(cudaFuncSetAttribute(qlinear_prefill_kn_kernel<TM, true, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES));
+        B200Q_CUDA_TRY(cudaFuncSetAttribute(qlinear_prefill_kn_kernel<TM, false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES));
         if (dev >= 0 && dev < 64) attr_set[dev] = true;
     }
-    if (p.ep.bias != nullptr || p.ep.residual != nullptr || p.ep.act != kActNone) {
-        qlinear_prefill_kn_kernel<TM, true><<<grid, THREADS, Cfg::SMEM_BYTES, stream>>>(map_w, map_a, p);
+    const bool fused = p.ep.bias != nullptr || p.ep.residual != nullptr || p.ep.act != kActNone;
+    if (weight_nk) {
+        if (fused) return set_error(B200Q_UNSUPPORTED, "qlinear: the fused epilogue is served for [K, N] weights");
+        qlinear_prefill_kn_kernel<TM, false, true><<<grid, THREADS, Cfg::SMEM_BYTES, stream>>>(map_w, map_a, p);
+    } else if (fused) {
+        qlinear_prefill_kn_kernel<TM, true, false><<<grid, THREADS, Cfg::SMEM_BYTES, stream>>>(map_w, map_a, p);
     } else {
-        qlinear_prefill_kn_kernel<TM, false><<<grid, THREADS, Cfg::SMEM_BYTES, stream>>>(map_w, map_a, p);
+        qlinear_prefill_kn_kernel<TM, false, false><<<grid, THREADS, Cfg::SMEM_BYTES, stream>>>(map_w, map_a, p);
     }
     B200Q_CHECK_LAUNCH("qlinear_prefill_kn_kernel");
     return B200Q_OK;
 }
 
+bool prefill_nk_supported(const void *a, const void *wq, int64_t N, int64_t K) {
+    return (N % 8 == 0) && (K % 16 == 0) && ((reinterpret_cast<uintptr_t>(a) & 15u) == 0) && ((reinterpret_cast<uintptr_t>(wq) & 15u) == 0);
+}
+
 int launch_prefill_kn(const void *a, const void *wq, const void *scale, void *c, int64_t M, int64_t N, int64_t K,
-                      cudaStream_t stream, const OutTargets *targets, const Epilogue *epilogue) {
+                      cudaStream_t stream, const OutTargets *targets, const Epilogue *epilogue, bool weight_nk) {
     int sms = sm_count();
     if (sms <= 0) sms = 148;
     switch (choose_tile_m(M, N, sms)) {
-        case 64: return launch_prefill_tm<64>(a, wq, scale, c, M, N, K, stream, targets, epilogue, sms);
-        default: return launch_prefill_tm<256>(a, wq, scale, c, M, N, K, stream, targets, epilogue, sms);
+        case 64: return launch_prefill_tm<64>(a, wq, scale, c, M, N, K, stream, targets, epilogue, sms, weight_nk);
+        default: return launch_prefill_tm<256>(a, wq, scale, c, M, N, K, stream, targets, epilogue, sms, weight_nk);
     }
 }
 

@@ -20,6 +20,7 @@ from .patterns import (
     SymmetricEmbeddingQuantizePattern,
     QuantizedLinearEpilogueFusion,
     quantized_matmul,
+    quantized_linear_nk,
     quantized_embedding,
     dequantized_weight,
 )

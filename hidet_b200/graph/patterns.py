@@ -30,6 +30,11 @@ def _fusable(k: int, n: int) -> bool:
     return n % 16 == 0 and k % 8 == 0
 
 
+def quantized_linear_nk(a: torch.Tensor, wq_nk: torch.Tensor, scale: torch.Tensor) -> torch.Tensor:
+    """The call made for a linear layer whose int8 weight was kept in torch's [N, K] layout."""
+    return quant.symmetric_quant_matmul(a, wq_nk, scale, weight_layout='NK')
+
+
 def quantized_matmul(a: torch.Tensor, wq: torch.Tensor, scale: torch.Tensor, bias: Optional[torch.Tensor] = None,
                      residual: Optional[torch.Tensor] = None, activation: Optional[str] = None) -> torch.Tensor:
     """The call the rewritten graph makes: the quantized matmul operator, resolved to the library kernel.
@@ -55,13 +60,28 @@ def _eligible(w: torch.Tensor) -> bool:
 
 
 class SymmetricLinearQuantizePattern(SubgraphRewriteRule):
-    def __init__(self, quant_type: str = 'int8', dims: Union[int, List[int]] = 0):
+    def __init__(self, quant_type: str = 'int8', dims: Union[int, List[int]] = 0, linear_weight_layout: str = 'KN'):
+        """linear_weight_layout: what becomes of a torch.nn.Linear / F.linear weight W[N, K].  'KN' (default):
+        transposed once at rewrite time into the reference's [K, N] layout, whose kernels take the fused
+        epilogue.  'NK': kept as it is and quantized per row (dims=1) -- the same codes and scales -- and run
+        by the [N, K] kernels; nothing is transposed, and the bias, if any, stays a separate add."""
         super().__init__('symmetric_linear_quantize')
         if quant_type != 'int8':
             raise ValueError('the fused quantized matmul takes int8 weights, got {}'.format(quant_type))
         if dims not in (0, [0]):
             raise ValueError('per-output-channel quantization of a [K, N] weight is dims=0, got {}'.format(dims))
+        if linear_weight_layout not in ('KN', 'NK'):
+            raise ValueError("linear_weight_layout must be 'KN' or 'NK', got {!r}".format(linear_weight_layout))
         self.quant_type = quant_type
+        self.linear_weight_layout = linear_weight_layout
+
+    def _install_nk(self, gm: fx.GraphModule, node: fx.Node, w_nk: torch.Tensor, idx: int):
+        wq, scale = quant.symmetric_quantize(w_nk.contiguous(), self.quant_type, dims=-1)
+        wq_name, scale_name = '_b200q_wq_{}'.format(idx), '_b200q_scale_{}'.format(idx)
+        gm.register_buffer(wq_name, wq)
+        gm.register_buffer(scale_name, scale)
+        with gm.graph.inserting_before(node):
+            return gm.graph.get_attr(wq_name), gm.graph.get_attr(scale_name)
 
     def _install(self, gm: fx.GraphModule, node: fx.Node, w_kn: torch.Tensor, idx: int):
         wq, scale = quant.symmetric_quantize(w_kn.contiguous(), self.quant_type, dims=0)
@@ -83,6 +103,18 @@ class SymmetricLinearQuantizePattern(SubgraphRewriteRule):
                 if not isinstance(mod, torch.nn.Linear) or not _eligible(mod.weight) or len(node.args) != 1:
                     continue
                 if mod.weight.shape[1] % 2 or mod.weight.shape[0] % 4:
+                    continue
+                if self.linear_weight_layout == 'NK':
+                    wq_node, scale_node = self._install_nk(gm, node, mod.weight.detach(), existing + count)
+                    with gm.graph.inserting_before(node):
+                        new = gm.graph.call_function(quantized_linear_nk, (node.args[0], wq_node, scale_node))
+                        if mod.bias is not None:
+                            bias_name = '_b200q_bias_{}'.format(existing + count)
+                            gm.register_buffer(bias_name, mod.bias.detach())
+                            new = gm.graph.call_function(torch.add, (new, gm.graph.get_attr(bias_name)))
+                    node.replace_all_uses_with(new)
+                    gm.graph.erase_node(node)
+                    count += 1
                     continue
                 wq_node, scale_node = self._install(gm, node, mod.weight.detach().t(), existing + count)
                 with gm.graph.inserting_before(node):
@@ -122,6 +154,16 @@ class SymmetricLinearQuantizePattern(SubgraphRewriteRule):
                     continue
                 w_nk = constants[w.name]
                 if w_nk.shape[1] % 2 or w_nk.shape[0] % 4:
+                    continue
+                if self.linear_weight_layout == 'NK':
+                    wq_node, scale_node = self._install_nk(gm, node, w_nk, existing + count)
+                    with gm.graph.inserting_before(node):
+                        new = gm.graph.call_function(quantized_linear_nk, (x, wq_node, scale_node))
+                        if bias is not None:
+                            new = gm.graph.call_function(torch.add, (new, bias))
+                    node.replace_all_uses_with(new)
+                    gm.graph.erase_node(node)
+                    count += 1
                     continue
                 wq_node, scale_node = self._install(gm, node, w_nk.t(), existing + count)
                 with gm.graph.inserting_before(node):

@@ -148,6 +148,28 @@ def test_two_step_graph_is_fused():
     assert torch.allclose(fused.float(), unfused.float(), atol=1e-2, rtol=1e-2)
 
 
+def test_linear_weights_can_stay_in_torch_layout():
+    model = TwoLinears().half().cuda().eval()
+    x = torch.randn(8, 256, generator=torch.Generator().manual_seed(2)).half().cuda()
+    gm = fx.symbolic_trace(model)
+    with hg.PassContext() as ctx:
+        ctx.add_quantize_rules([hg.SymmetricLinearQuantizePattern(linear_weight_layout='NK')])
+        hg.optimize(gm)
+    targets = [n.target for n in gm.graph.nodes if n.op == 'call_function']
+    assert targets.count(hg.quantized_matmul) == 1 and targets.count(hg.quantized_linear_nk) == 1
+    buffers = dict(gm.named_buffers())
+    assert tuple(buffers['_b200q_wq_1'].shape) == (128, 512)   # [N, K], as torch keeps it
+    # the same codes and scales as the transposed [K, N] weight quantized per column
+    wq_kn, scale_kn = hidet_b200.symmetric_quantize(model.fc.weight.detach().t().contiguous(), 'int8', dims=0)
+    assert torch.equal(buffers['_b200q_wq_1'], wq_kn.t()) and torch.equal(buffers['_b200q_scale_1'], scale_kn)
+    got = gm(x)
+    gm_kn = fx.symbolic_trace(model)
+    with hg.PassContext() as ctx:
+        ctx.add_quantize_rules([hg.SymmetricLinearQuantizePattern()])
+        hg.optimize(gm_kn)
+    assert (got.float() - gm_kn(x).float()).abs().max() < 2e-3
+
+
 def test_pass_without_int8_leaves_the_graph_alone():
     model = TwoLinears().half().cuda().eval()
     gm = fx.symbolic_trace(model)

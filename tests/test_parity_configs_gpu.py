@@ -101,7 +101,8 @@ def test_70b_down_projection_shape():
     assert ffi.func('b200q_check_status')() == ffi.OK
 
 
-@pytest.mark.parametrize('m,k,n', [(4, 512, 256), (16, 4096, 1024), (1, 4096, 4096), (64, 1024, 512), (300, 2048, 768), (5, 200, 48)])
+@pytest.mark.parametrize('m,k,n', [(4, 512, 256), (16, 4096, 1024), (1, 4096, 4096), (64, 1024, 512), (300, 2048, 768), (5, 200, 48), (16, 4096, 11008),
+                                   (8, 8192, 3584), (4, 16384, 256), (3, 1024, 136), (2, 64, 16)])
 def test_weight_layout_nk_against_the_oracle(m, k, n):
     w = seeded_weight(k, n, seed=k + n)
     wq, scale = oracle.symmetric_quantize(w, 'int8', 0)
@@ -119,6 +120,19 @@ def test_weight_layout_nk_against_the_oracle(m, k, n):
     # and it is the same function as the [K, N] layout on the transposed weight
     c_kn = hidet_b200.symmetric_quant_matmul(torch.from_numpy(a).cuda(), torch.from_numpy(wq).cuda(), torch.from_numpy(scale).cuda())
     assert (c.float() - c_kn.float()).abs().max().item() <= TIGHT_TOL * top
+    assert ffi.func('b200q_check_status')() == ffi.OK
+
+
+@pytest.mark.parametrize('m,k,n', [(2048, 4096, 4096), (2048, 11008, 4096), (65, 1024, 520), (513, 4096, 11008)])
+def test_weight_layout_nk_large_m_against_fp32_matmul(m, k, n):
+    wq, scale = device_weight(k, n, seed=k + n)
+    wq_nk = wq.t().contiguous()
+    a = device_activation(m, k, seed=m)
+    ref = fp32_reference(a, wq, scale)
+    c = hidet_b200.symmetric_quant_matmul(a, wq_nk, scale, weight_layout='NK')
+    assert_close(c, ref)
+    # the two layouts are the same function of the same numbers
+    assert_close(c, hidet_b200.symmetric_quant_matmul(a, wq, scale).float(), tol=1e-3)
     assert ffi.func('b200q_check_status')() == ffi.OK
 
 
