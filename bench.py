@@ -284,6 +284,23 @@ def extra_sections(torch, hidet_b200, device, stream, peaks):
     qbytes = 3 * k * n + 2 * n
     out['quantize'] = {'K': k, 'N': n, 'dtype': 'f16->i8, dims=0', 'us_per_launch': round(us, 2), 'GBps': round(qbytes / us / 1e3, 1),
                        'frac_of_hbm_peak': round(qbytes / us / 1e3 / peaks['hbm_gbs'], 4)}
+    del ws
+    # The 70B-shaped layer of the multi-GPU runs, unsharded on this one GPU: the base of their speed-up.
+    stack = make_quantized_stack(torch, hidet_b200, device, K_70B, N_70B, 2, seed=70)
+    one_gpu = []
+    for m in MS_70B:
+        gen = torch.Generator(device=device).manual_seed(4)
+        a = torch.randn(m, K_70B, generator=gen, device=device, dtype=torch.float32).to(torch.float16)
+        c = torch.empty(m, N_70B, dtype=torch.float16, device=device)
+
+        def fn70():
+            for wq, scale in stack:
+                hidet_b200.symmetric_quant_matmul(a, wq, scale, out=c)
+
+        us = time_graph(torch, stream, fn70, len(stack))
+        one_gpu.append({'M': m, 'K': K_70B, 'N': N_70B, 'us_per_layer_one_gpu': round(us, 2),
+                        'GBps': round(algorithmic_bytes(m, K_70B, N_70B) / us / 1e3, 1), 'TFLOPS': round(2.0 * m * K_70B * N_70B / us / 1e6, 1)})
+    out['sharded_70b_one_gpu'] = one_gpu
     return out
 
 
@@ -517,7 +534,7 @@ def main(argv=None) -> int:
     if args.impl == 'reference':
         return run_reference_arm(args)
     if args.gpus > 1 or int(os.environ.get('WORLD_SIZE', '1')) > 1:
-        from hidet_b200.bench_sharded import run_sharded
+        from bench_sharded import run_sharded
 
         return run_sharded(args)
     return run_single_gpu(args)

@@ -28,6 +28,9 @@ def run_sharded(args) -> int:
     import hidet_b200
     from hidet_b200.distributed import ColumnParallelQuantLinear, column_range
 
+    # Plain peer mappings only: the outputs are written with ordinary stores, and memory bound to an NVLink
+    # multicast object must not be left behind by a rank that ends early.
+    os.environ.setdefault('TORCH_SYMM_MEM_DISABLE_MULTICAST', '1')
     rank = int(os.environ.get('RANK', '0'))
     world = int(os.environ.get('WORLD_SIZE', str(args.gpus)))
     local_rank = int(os.environ.get('LOCAL_RANK', str(rank)))
@@ -44,11 +47,7 @@ def run_sharded(args) -> int:
     if getattr(args, 'm_list', None):
         MS_70B = tuple(int(x) for x in args.m_list.split(','))
     if args.gather is None:
-        # Peer stores and peer copies are the faster delivery and the default up to four GPUs, where they
-        # have been measured.  On eight GPUs the last run of that path ended in a launch failure, before a
-        # fault in the large-M kernel's barriers was found and fixed; it has not been run there since, so
-        # eight GPUs default to the NCCL all-gather, which has.
-        args.gather = 'p2p' if world <= 4 else 'nccl'
+        args.gather = 'p2p'  # epilogue stores into the peer-mapped outputs; 'nccl' is the all-gather of the reference's op
     begin, end = column_range(n, rank, world)
     n_local = end - begin
     copies = max(2, -(-(2 * 128 * 1024 * 1024) // (k * n_local)))
@@ -90,6 +89,26 @@ def run_sharded(args) -> int:
     for _ in range(max(args.warmup, 3)):
         step()
     torch.cuda.synchronize()
+
+    # Parity of the delivered result: the gathered [M, N] output of the first weight on this rank against the
+    # same layer computed shard by shard on this GPU alone (every rank draws the full weight from the seed).
+    gen = torch.Generator(device=device).manual_seed(100)
+    w_full = (torch.randn(k, n, generator=gen, device=device, dtype=torch.float32) * 0.02).to(torch.float16)
+    parity_ok = True
+    for m in MS_70B:
+        got = layers[0](acts[m]).clone()
+        want = torch.empty(m, n, dtype=torch.float16, device=device)
+        for r in range(world):
+            b, e = column_range(n, r, world)
+            wq_r, scale_r = hidet_b200.symmetric_quantize(w_full[:, b:e].contiguous(), 'int8', dims=0)
+            want[:, b:e] = hidet_b200.symmetric_quant_matmul(acts[m], wq_r, scale_r)
+        torch.cuda.synchronize()
+        parity_ok = parity_ok and bool(torch.equal(got, want))
+    del w_full
+    flag = torch.tensor([1 if parity_ok else 0], device=device)
+    dist.all_reduce(flag, op=dist.ReduceOp.MIN)
+    parity_ok = bool(flag.item())
+    assert parity_ok, 'the gathered output differs from the shard-by-shard result'
 
     # Replay each sweep as one CUDA graph when the whole step can be captured (kernel launches and the
     # cross-rank barrier are ordinary stream work); otherwise launch eagerly.
@@ -149,8 +168,17 @@ def run_sharded(args) -> int:
         def local_only():
             for layer in layers:
                 layer.local(acts[m], out=c_local)
-        us_local = timed(local_only, 5) * 1e3 / copies
+
+        local_only()
+        g_local = None
+        if graphs:
+            torch.cuda.current_stream().synchronize()
+            g_local = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g_local, stream=torch.cuda.current_stream()):
+                local_only()
+        us_local = timed((lambda: g_local.replay()) if g_local is not None else local_only, 5) * 1e3 / copies
         shapes[-1]['us_local_kernel'] = round(us_local, 2)
+        del g_local
 
     # The same layer, unsharded, on this GPU alone (every rank does it at once, without communication; rank 0's
     # time is reported): what the sharded layer is to be compared with.
@@ -207,25 +235,32 @@ def run_sharded(args) -> int:
             'metric': 'quant-linear HBM GB/s (70B-shaped layer, column-parallel)', 'value': value, 'unit': 'GB/s', 'n_gpus': world,
             'steps': args.steps, 'warmup': max(args.warmup, 3), 'ms_per_step': ms_per_step, 'higher_is_better': True,
             'scaling': 'strong', 'vs_baseline': None, 'dtype': 'f16', 'accumulate': 'f32', 'weight_dtype': 'i8', 'data': 'synthetic',
-            'config': {'workload': 'sharded-70b-layer', 'K': k, 'N': n, 'M': list(MS_70B), 'parallelism': 'tp{} (columns), outputs by {}'.format(world, 'peer stores from the epilogue (M <= 32) or peer copies after the kernel, + barrier' if args.gather == 'p2p' else 'NCCL all-gather'),
+            'config': {'workload': 'sharded-70b-layer', 'K': k, 'N': n, 'M': list(MS_70B), 'parallelism': 'tp{} (columns), outputs by {}'.format(world, 'peer stores from the kernels\' epilogues + one cross-rank barrier' if args.gather == 'p2p' else 'NCCL all-gather'),
                        'weights_in_rotation': copies, 'l2': 'inputs larger than L2: {} distinct weight shards of {} MB per rank'.format(copies, k * n_local // 1000000),
                        'timing': timing + ', CUDA events, barrier on both sides, max over ranks'},
             'tflops': flops_per_step / (ms_per_step * 1e-3) / 1e12,
-            'gpu_launches': sum(2 if (args.gather == 'p2p' and m >= ColumnParallelQuantLinear.SPLIT_ROWS_FROM) else 1 for m in MS_70B) * copies * args.steps,
+            'gpu_launches': len(MS_70B) * copies * args.steps,
+            'parity_checked': parity_ok,
             'clocks': clocks.summary(),
             'roofline': {'bound': 'hbm for M <= 16, tensor for M >= 256', 'achieved': value, 'peak': peaks['hbm_gbs'] * world, 'unit': 'GB/s',
                          'frac': value / (peaks['hbm_gbs'] * world), 'traffic': None, 'peak_source': peaks['source'] + ' (burst copy) x n_gpus',
-                         'kernel': 'qlinear_decode_kn_kernel / qlinear_prefill_kn_kernel' + (' + ncclAllGather' if args.gather == 'nccl' else ' + peer copies')},
+                         'kernel': 'qlinear_decode_kn_kernel / qlinear_prefill_kn_kernel' + (' + ncclAllGather' if args.gather == 'nccl' else ' (peer stores)')},
             'shapes': shapes,
             'e2e': {'value': e2e_value, 'unit': 'GB/s', 'h2d_bytes_per_step': sum(t.numel() * 2 for t in pinned_in.values()),
                     'd2h_bytes_per_step': sum(t.numel() * 2 for t in pinned_out.values()), 'ms_per_step': e2e_ms},
         }
         line['speedup_vs_one_gpu'] = round(sum(one_gpu) / sum(e['us_per_layer'] for e in shapes), 2)
         print(json.dumps(line), flush=True)
-    # Captured collectives keep the communicator alive: release the graphs before the process group.
+    # Captured collectives keep the communicator alive, and peer-mapped outputs must not outlive a rank:
+    # release the graphs and everything that maps another GPU's memory before the process group goes.
     import gc
 
     graphs.clear()
+    torch.cuda.synchronize()
+    dist.barrier()
+    for layer in layers:
+        layer.release()
+    layers.clear()
     gc.collect()
     torch.cuda.synchronize()
     dist.barrier()

@@ -144,14 +144,7 @@ B200Q_API int b200q_qlinear_f16_i8_to_peers(const void *a, const void *wq, const
     if (!decode_kn_supported(a, wq, N, K)) {
         return set_error(B200Q_UNSUPPORTED, "qlinear_f16_i8_to_peers: operands need 16-byte aligned bases and rows (N %% 16 == 0, K %% 8 == 0)");
     }
-    if (use_prefill_kernel(M, N, K)) {
-        // The large-M kernel writes one destination.  With several, a caller runs it into its own buffer
-        // (n_dst = 1, with ldc and col_offset) and copies the columns to the others.
-        if (n_dst > 1) {
-            return set_error(B200Q_UNSUPPORTED, "qlinear_f16_i8_to_peers: M = %lld is served by the large-M kernel, which stores to one destination; pass n_dst = 1 and copy the columns to the other ranks", (long long)M);
-        }
-        return launch_prefill_kn(a, wq, scale, dst[0], M, N, K, s, &t);
-    }
+    if (use_prefill_kernel(M, N, K)) return launch_prefill_kn(a, wq, scale, dst[0], M, N, K, s, &t);
     return launch_decode_kn(a, wq, scale, dst[0], M, N, K, 0, K, true, workspace, workspace_bytes, s, &t);
 }
 

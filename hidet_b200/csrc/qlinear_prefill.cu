@@ -17,8 +17,9 @@
 //               accumulators; tcgen05.commit frees the stage / publishes the accumulator
 //   warps 0-3   epilogue: tcgen05.ld of the accumulator (lane = weight column n, column = row m),
 //               times scale[n], one rounding to f16, transposed through a small staging buffer and
-//               written as 256-byte rows with 16-byte stores to C[m, n] (one destination, which may be a
-//               column range of a wider matrix); overlaps the next tile's MMAs
+//               written as 256-byte rows with 16-byte stores to C[m, n] of every destination (each may be a
+//               column range of a wider matrix; the destinations of a column-parallel layer are the
+//               peer-mapped outputs of all ranks); overlaps the next tile's MMAs
 // Rows beyond M, columns beyond N and k beyond K are zero-filled by TMA and never stored.
 //
 // Every wait is bounded: a wait that runs out records where in the device status word, the role
@@ -410,7 +411,11 @@ __global__ void __launch_bounds__(THREADS, 1) qlinear_prefill_kn_kernel(const __
                     const int m = cb * 32 + r;
                     if (m < m_left && cols_ok) {
                         const uint4 val = *reinterpret_cast<const uint4 *>(staging + r * STAGE_ROW_BYTES + chunk * 16);
-                        *reinterpret_cast<uint4 *>(static_cast<__half *>(p.out.ptr[0]) + (size_t)(m0 + m) * p.out.ldc + col_off) = val;
+                        const size_t off = (size_t)(m0 + m) * p.out.ldc + col_off;
+                        // every destination: this GPU's output and, for a column-parallel layer, the peer-mapped
+                        // outputs of the other ranks (plain 16-byte stores over NVLink, no loads)
+#pragma unroll 1
+                        for (int d = 0; d < p.out.count; ++d) *reinterpret_cast<uint4 *>(static_cast<__half *>(p.out.ptr[d]) + off) = val;
                     }
                 }
                 asm volatile("bar.sync 1, 128;" ::: "memory");  // staging may be overwritten
@@ -484,8 +489,8 @@ static int launch_prefill_tm(const void *a, const void *wq, const void *scale, v
     }
     if (epilogue != nullptr) p.ep = *epilogue;
     if (p.ep.act == kActSiluMul && N % 16 != 0) return set_error(B200Q_INVALID_ARGUMENT, "qlinear: the gate / up pairing needs N to be a multiple of 16, got %lld", (long long)N);
-    if (p.out.count != 1) return set_error(B200Q_UNSUPPORTED, "qlinear: the large-M kernel stores to one destination, got %d", p.out.count);
-    if ((reinterpret_cast<uintptr_t>(p.out.ptr[0]) & 15u) != 0) return set_error(B200Q_INVALID_ARGUMENT, "qlinear: output is not 16-byte aligned");
+    for (int d = 0; d < p.out.count; ++d)
+        if ((reinterpret_cast<uintptr_t>(p.out.ptr[d]) & 15u) != 0) return set_error(B200Q_INVALID_ARGUMENT, "qlinear: output %d is not 16-byte aligned", d);
     if (p.out.ldc % 8 != 0 || p.out.col0 % 8 != 0) return set_error(B200Q_INVALID_ARGUMENT, "qlinear: output row length and column offset must be multiples of 8 elements");
     p.status = device_status_word();
     p.M = (int)M;

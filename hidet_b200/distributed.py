@@ -69,17 +69,6 @@ def gather_columns(c_local: torch.Tensor, group=None, out: Optional[torch.Tensor
     return out
 
 
-_SIDE_STREAMS = {}
-
-
-def _side_stream(device: torch.device) -> 'torch.cuda.Stream':
-    """The stream (one per device) on which copies to the peers run beside the kernels."""
-    index = device.index if device.index is not None else torch.cuda.current_device()
-    if index not in _SIDE_STREAMS:
-        _SIDE_STREAMS[index] = torch.cuda.Stream(torch.device('cuda', index))
-    return _SIDE_STREAMS[index]
-
-
 class PeerOutput:
     """A [rows, cols] float16 output buffer that exists on every rank of the group and that every
     rank can store into directly: symmetric memory (torch.distributed._symmetric_memory), i.e. the
@@ -100,6 +89,12 @@ class PeerOutput:
             self.ptr_tables.append([int(p) for p in handle.buffer_ptrs])
         self.turn = 0
 
+    def release(self) -> None:
+        """Drops the buffers, handles and pointer tables.  Call it on every rank before the process group is
+        destroyed (and before a rank exits), while no kernel that stores to a peer is in flight: memory that
+        is still peer-mapped when its owner goes away faults the GPUs that map it."""
+        self.buffers, self.handles, self.ptr_tables = [], [], []
+
     def next(self):
         """(local buffer, table of every rank's pointer to its copy, handle) for the next result."""
         i = self.turn
@@ -115,19 +110,12 @@ class ColumnParallelQuantLinear:
 
     gather='nccl'  the local kernel writes its slice, an NCCL all-gather collects the slices
                    (rank-major, as the reference's all-gather op) and one copy puts them side by side;
-    gather='p2p'   every rank's [M, N] output is peer-mapped on all ranks (symmetric memory).  For small M
-                   the kernel's epilogue stores its columns straight into every rank's output over NVLink
-                   (b200q_qlinear_f16_i8_to_peers); for large M the kernel writes its columns of the local
-                   output and the copy engines push them to the other ranks (b200q_push_columns), one
-                   half of the rows while the other half is computed.  One cross-rank barrier
-                   on the stream follows: no staging buffer, no reshuffle, no collective launch.
+    gather='p2p'   every rank's [M, N] output is peer-mapped on all ranks (symmetric memory), and the kernel's
+                   epilogue stores its columns straight into every rank's output over NVLink, tile by tile
+                   while the rest of the product is still being computed (b200q_qlinear_f16_i8_to_peers).
+                   One cross-rank barrier on the stream follows: no staging buffer, no reshuffle, no
+                   collective launch.
     """
-
-    # Largest row count whose result is stored to the peers from the kernel's epilogue (the small-M
-    # kernel).  Above it the columns are pushed by copies after the kernel.
-    FUSED_STORE_MAX_ROWS = 32
-    # Row count from which the large-M path runs as two halves, so that pushing one overlaps computing the other.
-    SPLIT_ROWS_FROM = 1024
 
     def __init__(self, wq_shard: torch.Tensor, scale_shard: torch.Tensor, group=None, gather: str = 'nccl'):
         if wq_shard.dtype != torch.int8 or wq_shard.dim() != 2:
@@ -156,6 +144,13 @@ class ColumnParallelQuantLinear:
         """Use `other`'s peer-mapped output buffers (layers of equal width that run one after the
         other can share them; every layer that owns its own costs two [M, N] buffers per shape)."""
         self._peer_outputs = other._peer_outputs
+
+    def release(self) -> None:
+        """Gives up the peer-mapped outputs and gather buffers (see PeerOutput.release)."""
+        for peer_out in self._peer_outputs.values():
+            peer_out.release()
+        self._peer_outputs = {}
+        self._buffers = {}
 
     @property
     def in_features(self) -> int:
@@ -193,26 +188,9 @@ class ColumnParallelQuantLinear:
             ws_bytes = ffi.func('b200q_qlinear_workspace_bytes')(rows, n_local, k, ffi.LAYOUT_KN)
             ws_ptr, ws_size = workspaces.get(x.device, ws_bytes)
             main = torch.cuda.current_stream(x.device)
-            if rows <= self.FUSED_STORE_MAX_ROWS:
-                table = (ctypes.c_void_p * self.world)(*ptrs)
-                qlinear(x.data_ptr(), self.wq.data_ptr(), self.scale.data_ptr(), table, self.world, n, c0, rows, n_local, k,
-                        ws_ptr, ws_size, main.cuda_stream)
-            else:
-                # Rows in two halves when there are enough of them: the copy engines push the first half to
-                # the peers while the SMs compute the second.
-                pieces = 2 if rows >= self.SPLIT_ROWS_FROM else 1
-                bounds = [rows * i // pieces // 8 * 8 for i in range(pieces)] + [rows]
-                side = _side_stream(x.device)
-                # the other ranks, the next one first, so that the ranks do not all push to the same one
-                others = [ptrs[(self.rank + step) % self.world] for step in range(1, self.world)]
-                for r0, r1 in zip(bounds[:-1], bounds[1:]):
-                    own = (ctypes.c_void_p * 1)(ptrs[self.rank] + r0 * n * 2)
-                    qlinear(x.data_ptr() + r0 * k * 2, self.wq.data_ptr(), self.scale.data_ptr(), own, 1, n, c0, r1 - r0, n_local, k,
-                            ws_ptr, ws_size, main.cuda_stream)
-                    side.wait_stream(main)
-                    table = (ctypes.c_void_p * len(others))(*[p + r0 * n * 2 for p in others])
-                    ffi.func('b200q_push_columns')(ptrs[self.rank] + r0 * n * 2, table, len(others), r1 - r0, n_local, n, c0, side.cuda_stream)
-                main.wait_stream(side)
+            table = (ctypes.c_void_p * self.world)(*ptrs)
+            qlinear(x.data_ptr(), self.wq.data_ptr(), self.scale.data_ptr(), table, self.world, n, c0, rows, n_local, k,
+                    ws_ptr, ws_size, main.cuda_stream)
             handle.barrier(channel=0)  # on the current stream: every rank's columns have landed everywhere
         return out.view(lead + (n,))
 

@@ -185,15 +185,16 @@ B200Q_API int b200q_qlinear_f16_i8_parts(const void *a, const void *wq, const vo
  * python/hidet/graph/ops/distributed.py:63-97 (whose result is rank-major and needs a reshuffle).
  * The caller orders the ranks afterwards (a barrier between "all kernels done" and "outputs read").
  * `dst` is a host array.  KN layout; workspace as for b200q_qlinear_f16_i8 with the same M, N, K.
- * Several destinations are served for M <= 32 (the small-M kernel); for larger M the call returns
- * B200Q_UNSUPPORTED unless n_dst == 1: run it into this rank's own buffer and copy the columns on.
+ * Both kernels store to every destination from their epilogue, tile by tile, so the delivery overlaps
+ * the rest of the product; ldc and col_offset must be multiples of 8 and the destinations 16-byte aligned
+ * when the large-M kernel serves the call.
  */
 B200Q_API int b200q_qlinear_f16_i8_to_peers(const void *a, const void *wq, const void *scale, void *const *dst, int n_dst,
                                             int64_t ldc, int64_t col_offset, int64_t M, int64_t N, int64_t K, void *workspace,
                                             size_t workspace_bytes, void *stream);
 
 /*
- * The second half of the column-parallel layer for large M: copies columns
+ * Delivery by copies instead of epilogue stores (an alternative, not what the layer uses): copies columns
  * [col_offset, col_offset + cols) of the fp16 matrix src[rows, ld] into the same place of every
  * dst[i][rows, ld] (pointers valid on this device, peer-mapped for other GPUs; an entry equal to src
  * is skipped).  One strided device-to-device copy per destination, executed by the copy engines in

@@ -14,6 +14,7 @@ def main() -> int:
     import hidet_b200
     from hidet_b200.distributed import ColumnParallelQuantLinear, column_range
 
+    os.environ.setdefault('TORCH_SYMM_MEM_DISABLE_MULTICAST', '1')   # plain peer mappings only
     rank, world = int(os.environ['RANK']), int(os.environ['WORLD_SIZE'])
     local = int(os.environ.get('LOCAL_RANK', rank))
     torch.cuda.set_device(local)
@@ -28,7 +29,7 @@ def main() -> int:
             for gather in ('nccl', 'p2p'):
                 layer = ColumnParallelQuantLinear.from_weight_shard(w[:, begin:end].contiguous(), gather=gather)
                 assert torch.equal(layer.wq, wq_full[:, begin:end]) and torch.equal(layer.scale, scale_full[begin:end])
-                for m in (1, 16, 40, 300):
+                for m in (1, 16, 40, 300, 1100):
                     x = torch.randn(m, k, generator=gen, device=device).half()
                     # The split of K over CTAs depends on the width, so a shard's sums are taken in another
                     # order than the full layer's: bit-exact against the shards computed one by one on this
@@ -45,6 +46,9 @@ def main() -> int:
                         assert got.shape == want.shape
                         assert torch.equal(got, want), 'rank {} gather {} M {} call {}: {} differ'.format(
                             rank, gather, m, call, int((got != want).sum()))
+                torch.cuda.synchronize()
+                dist.barrier()
+                layer.release()   # nothing peer-mapped may outlive the group
         assert hidet_b200.ffi.func('b200q_check_status')() == 0
         dist.barrier()
         if rank == 0:
