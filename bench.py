@@ -38,22 +38,67 @@ K_DECODE = 4096
 DECODE_NS = (4096, 11008)
 DECODE_MS = (1, 4, 16)
 STACK = {4096: 16, 11008: 6}  # distinct weight matrices per width: 268 MB + 270 MB of int8
-# dram__bytes_read.sum + dram__bytes_write.sum of one launch of the small-M kernel, from an ncu capture of
-# `bench.py --case M,4096,N --launches 8 --eager` (summary: profiles/qlinear_decode_kn_kernel.md); keyed (M, N).
-# The output stays in L2, so the write counter reads 0 to 9 KB.
-NCU_DRAM_BYTES = {(1, 4096): 16825088, (16, 4096): 16951552, (1, 11008): 45155072, (16, 11008): 45285632}
+TRAFFIC_FILE = os.path.join(ROOT, 'profiles', 'qlinear_decode_dram_traffic.json')
+DECODE_SOURCE = os.path.join(ROOT, 'hidet_b200', 'csrc', 'qlinear_decode.cu')
 
 
-def ncu_traffic_per_launch() -> float:
-    """Average DRAM traffic per launch over the launch mix of one step; M = 4 was not captured and is taken
-    on the line between M = 1 and M = 16."""
-    total, launches = 0.0, 0
-    for n, count in STACK.items():
-        lo, hi = NCU_DRAM_BYTES[(1, n)], NCU_DRAM_BYTES[(16, n)]
-        for m in DECODE_MS:
-            total += count * (lo + (hi - lo) * (m - 1) / 15.0)
-            launches += count
-    return total / launches
+def source_digest(path: str = DECODE_SOURCE) -> str:
+    import hashlib
+
+    with open(path, 'rb') as f:
+        return hashlib.sha256(f.read()).hexdigest()[:16]
+
+
+def record_traffic(csv_paths) -> int:
+    """Reads ncu CSV logs of `bench.py --case M,K,N --eager` captures (metrics dram__bytes_read.sum and
+    dram__bytes_write.sum of the small-M kernel; the case is taken from the file name, decode_M,K,N.csv) and
+    writes profiles/qlinear_decode_dram_traffic.json: DRAM bytes per launch by shape, with the digest of the
+    kernel source they were measured on."""
+    import csv
+    import re
+
+    per_case = {}
+    for path in csv_paths:
+        m = re.search(r'(\d+),(\d+),(\d+)', os.path.basename(path))
+        if not m:
+            raise SystemExit('cannot tell the case from the file name {}'.format(path))
+        launches = {}
+        with open(path, newline='') as f:
+            for row in csv.reader(f):
+                if len(row) >= 15 and row[12] in ('dram__bytes_read.sum', 'dram__bytes_write.sum') and 'qlinear_decode' in row[4]:
+                    scale = {'byte': 1, 'Kbyte': 1e3, 'Mbyte': 1e6, 'Gbyte': 1e9}[row[13]]
+                    launches.setdefault(row[0], 0.0)
+                    launches[row[0]] += float(row[14].replace(',', '')) * scale
+        if not launches:
+            raise SystemExit('no DRAM counters of the small-M kernel in {}'.format(path))
+        per_case['{},{},{}'.format(*m.groups())] = sum(launches.values()) / len(launches)
+    with open(TRAFFIC_FILE, 'w') as f:
+        json.dump({'kernel_source_sha256_16': source_digest(), 'unit': 'bytes per launch (dram__bytes_read.sum + dram__bytes_write.sum)',
+                   'cases': per_case}, f, indent=1)
+        f.write('\n')
+    print('wrote', TRAFFIC_FILE)
+    return 0
+
+
+def ncu_traffic_per_launch():
+    """Average DRAM traffic per launch over the launch mix of one step, from the recorded ncu capture of the kernel
+    as it is now: None when there is no record, when it was taken on another version of the kernel source, or when
+    a shape is missing (M = 4 was not captured and is taken on the line between M = 1 and M = 16)."""
+    try:
+        with open(TRAFFIC_FILE) as f:
+            rec = json.load(f)
+        if rec.get('kernel_source_sha256_16') != source_digest():
+            return None
+        total, launches = 0.0, 0
+        for n, count in STACK.items():
+            lo, hi = rec['cases']['1,{},{}'.format(K_DECODE, n)], rec['cases']['16,{},{}'.format(K_DECODE, n)]
+            for m in DECODE_MS:
+                total += count * rec['cases'].get('{},{},{}'.format(m, K_DECODE, n), lo + (hi - lo) * (m - 1) / 15.0)
+                launches += count
+        return total / launches
+    except (OSError, KeyError, ValueError):
+        return None
+
 
 K_70B, N_70B = 8192, 28672
 MS_70B = (1, 16, 256, 2048)
@@ -428,6 +473,11 @@ def run_single_gpu(args) -> int:
         with torch.cuda.stream(side):
             extras = extra_sections(torch, hidet_b200, device, side, peaks)
 
+    if not args.no_extras and not args.no_config4:
+        import bench_decoder
+
+        torch.cuda.empty_cache()
+        extras['config4'] = bench_decoder.run_config(bench_decoder.LLAMA_7B)
     status = hidet_b200.ffi.func('b200q_check_status')()
     assert status == 0
 
@@ -442,7 +492,9 @@ def run_single_gpu(args) -> int:
         'gpu_launches': launches_per_step * args.steps,
         'clocks': clocks.summary(),
         'roofline': {'bound': 'hbm', 'achieved': value, 'peak': peaks['hbm_gbs'], 'unit': 'GB/s', 'frac': value / peaks['hbm_gbs'],
-                     'traffic': ncu_traffic_per_launch(), 'traffic_unit': 'bytes per launch (ncu, average over the step\'s launch mix)',
+                     'traffic': ncu_traffic_per_launch(),
+                     'traffic_unit': 'DRAM bytes per launch from the recorded ncu capture of this kernel source, averaged over the step\'s launch mix; '
+                                     'null: no capture of the kernel as it is now (algorithmic_bytes_per_launch is the algorithmic figure)',
                      'algorithmic_bytes_per_launch': bytes_per_step / launches_per_step,
                      'peak_source': peaks['source'] + ' (burst copy)', 'kernel': 'qlinear_decode_kn_kernel'},
         'shapes': shapes,
@@ -524,13 +576,24 @@ def main(argv=None) -> int:
     ap.add_argument('--gather', choices=['nccl', 'p2p'], default=None,
                     help='multi-GPU: how output slices reach every rank (default: p2p up to four GPUs, nccl on eight)')
     ap.add_argument('--m-list', default=None, help='multi-GPU: comma-separated activation row counts to sweep instead of 1,16,256,2048')
+    ap.add_argument('--record-traffic', nargs='+', default=None, metavar='CSV',
+                    help='no benchmark: read ncu CSV logs (decode_M,K,N.csv) and write profiles/qlinear_decode_dram_traffic.json')
+    ap.add_argument('--config4', action='store_true', help='run only the Llama-2-7B-shaped decoder (512-token prompt, 128 greedy steps) and print its block')
+    ap.add_argument('--no-config4', action='store_true', help='leave the decoder block out of the default line')
     ap.add_argument('--case', default=None, help='M,K,N: time one shape only (small case for profiling and tuning)')
     ap.add_argument('--layout', choices=['KN', 'NK'], default='KN', help='weight layout for --case')
     ap.add_argument('--launches', type=int, default=200, help='launches to time for --case')
     ap.add_argument('--eager', action='store_true', help='launch one by one instead of replaying a CUDA graph (--case and multi-GPU)')
     args = ap.parse_args(argv)
+    if args.record_traffic:
+        return record_traffic(args.record_traffic)
     if args.case:
         return run_case(args)
+    if args.config4:
+        import bench_decoder
+
+        print(json.dumps({'config4': bench_decoder.run_config(bench_decoder.LLAMA_7B)}))
+        return 0
     if args.impl == 'reference':
         return run_reference_arm(args)
     if args.gpus > 1 or int(os.environ.get('WORLD_SIZE', '1')) > 1:

@@ -22,8 +22,11 @@
 //               peer-mapped outputs of all ranks); overlaps the next tile's MMAs
 // Rows beyond M, columns beyond N and k beyond K are zero-filled by TMA and never stored.
 //
-// Every wait is bounded: a wait that runs out records where in the device status word, the role
-// leaves its loops, and the CTA still releases its tensor memory and returns.
+// Every wait is bounded.  A wait that runs out records where in the device status word and raises a
+// CTA-wide abort flag that every other wait watches, so all roles leave their loops at once instead of
+// each running into its own limit.  Before the CTA gives back its tensor memory and retires, the producer
+// waits (bounded again) for every copy it has armed and the MMA lane for a final commit, so that nothing
+// still writes to shared memory or reads tensor memory when the CTA is gone.
 //
 // Replaces, for large M, the generated mma.sync kernel of
 // python/hidet/graph/ops/quant/matmul_f16_i8.py:136-485 (f16 accumulation) and the separate sum over
@@ -167,7 +170,9 @@ __global__ void __launch_bounds__(THREADS, 1) qlinear_prefill_kn_kernel(const __
     __shared__ __align__(8) uint64_t slot_free[STAGES];     // the MMAs that read the stage have completed
     __shared__ __align__(8) uint64_t acc_full[2];           // an accumulator holds a finished tile
     __shared__ __align__(8) uint64_t acc_empty[2];          // the four epilogue warps have read it out
+    __shared__ __align__(8) uint64_t drain_bar;             // every MMA issued has completed (teardown)
     __shared__ uint32_t tmem_base_slot;
+    __shared__ int abort_flag;                               // a wait ran out somewhere in this CTA
 
     const uint32_t smem_base = (smem_u32(smem_dyn) + 1023u) & ~1023u;  // swizzled operands need 1024-byte alignment
     unsigned char *smem_gen = smem_dyn + (smem_base - smem_u32(smem_dyn));
@@ -196,6 +201,8 @@ __global__ void __launch_bounds__(THREADS, 1) qlinear_prefill_kn_kernel(const __
             mbar_init(smem_u32(&acc_full[b]), 1);
             mbar_init(smem_u32(&acc_empty[b]), 4);
         }
+        mbar_init(smem_u32(&drain_bar), 1);
+        abort_flag = 0;
         mbar_fence_init();
     }
     if (warp == MMA_WARP) {
@@ -206,6 +213,16 @@ __global__ void __launch_bounds__(THREADS, 1) qlinear_prefill_kn_kernel(const __
     __syncthreads();
     tc_fence_after_sync();
     const uint32_t tmem_base = tmem_base_slot;
+    // Bounded wait that also ends when another role has given up; the role whose own limit runs out reports it.
+    auto wait = [&](uint32_t bar, uint32_t parity, unsigned int site) -> bool {
+        for (uint32_t i = 0; i < kSpinLimit; ++i) {
+            if (mbar_try_wait(bar, parity)) return true;
+            if (*reinterpret_cast<volatile int *>(&abort_flag) != 0) return false;
+        }
+        report_timeout(p.status, kKernelPrefill, site);
+        atomicExch(&abort_flag, 1);
+        return false;
+    };
 
     if (warp == PRODUCER_WARP) {
         // ---------------- TMA producer ----------------
@@ -215,31 +232,42 @@ __global__ void __launch_bounds__(THREADS, 1) qlinear_prefill_kn_kernel(const __
             const uint64_t keep = l2_policy_evict_last();  // both operands are re-read by other tiles: keep them in L2
             uint32_t i = 0;
             bool ok = true;
+            int last_raw[RAW_SLOTS], last_act[STAGES];  // the latest stage copied into each slot (-1: none)
+            for (int r = 0; r < RAW_SLOTS; ++r) last_raw[r] = -1;
+            for (int s = 0; s < STAGES; ++s) last_act[s] = -1;
             for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
                 const int n0 = (tile % p.n_tiles) * TN;
                 const int m0 = (tile / p.n_tiles) * TM;
                 for (int kb = 0; kb < k_blocks; ++kb, ++i) {
                     const int r = i % RAW_SLOTS;
                     const uint32_t use_r = i / RAW_SLOTS;
-                    if (use_r >= 1 && !mbar_wait(smem_u32(&raw_empty[r]), (use_r - 1) & 1)) {
-                        report_timeout(p.status, kKernelPrefill, 1);
+                    if (use_r >= 1 && !wait(smem_u32(&raw_empty[r]), (use_r - 1) & 1, 1)) {
                         ok = false;
                         break;
                     }
                     const uint32_t raw_bar = smem_u32(&raw_full[r][i % CONV_GROUPS]);  // the group that converts stage i
                     mbar_expect_tx(raw_bar, RAW_BYTES);
                     tma_load_2d_hint(raw_addr(r), &map_w, NK ? kb * BK : n0, NK ? n0 : kb * BK, raw_bar, keep);
+                    last_raw[r] = (int)i;
                     const int s = i % STAGES;
                     const uint32_t use = i / STAGES;
-                    if (use >= 1 && !mbar_wait(smem_u32(&slot_free[s]), (use - 1) & 1)) {
-                        report_timeout(p.status, kKernelPrefill, 6);
+                    if (use >= 1 && !wait(smem_u32(&slot_free[s]), (use - 1) & 1, 6)) {
                         ok = false;
                         break;
                     }
                     mbar_expect_tx(smem_u32(&act_full[s]), Cfg::ACT_BYTES);
                     tma_load_2d_hint(act_addr(s), &map_a, kb * BK, m0, smem_u32(&act_full[s]), keep);
+                    last_act[s] = (int)i;
                 }
             }
+            // Teardown: every copy this lane has armed must have landed before the CTA may retire.  After a
+            // normal run they all have (their stages were consumed); after an abort this waits for the stragglers.
+            for (int r = 0; r < RAW_SLOTS; ++r)
+                if (last_raw[r] >= 0 && !mbar_wait(smem_u32(&raw_full[r][last_raw[r] % CONV_GROUPS]), (uint32_t)(last_raw[r] / RAW_PERIOD) & 1))
+                    report_timeout(p.status, kKernelPrefill, 7);
+            for (int s = 0; s < STAGES; ++s)
+                if (last_act[s] >= 0 && !mbar_wait(smem_u32(&act_full[s]), (uint32_t)(last_act[s] / STAGES) & 1))
+                    report_timeout(p.status, kKernelPrefill, 7);
         }
     } else if (warp == MMA_WARP) {
         // ---------------- MMA issuer ----------------
@@ -248,17 +276,13 @@ __global__ void __launch_bounds__(THREADS, 1) qlinear_prefill_kn_kernel(const __
             bool ok = true;
             for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, ++t_iter) {
                 const uint32_t buf = t_iter & 1, acc_use = t_iter >> 1;
-                if (acc_use >= 1 && !mbar_wait(smem_u32(&acc_empty[buf]), (acc_use - 1) & 1)) {
-                    report_timeout(p.status, kKernelPrefill, 2);
-                    break;
-                }
+                if (acc_use >= 1 && !wait(smem_u32(&acc_empty[buf]), (acc_use - 1) & 1, 2)) break;
                 tc_fence_after_sync();
                 const uint32_t d_addr = tmem_base + buf * TM;
                 for (int kb = 0; kb < k_blocks; ++kb, ++i) {
                     const int s = i % STAGES;
                     const uint32_t use = i / STAGES;
-                    if (!mbar_wait(smem_u32(&act_full[s]), use & 1) || !mbar_wait(smem_u32(&conv_full[s]), use & 1)) {
-                        report_timeout(p.status, kKernelPrefill, 3);
+                    if (!wait(smem_u32(&act_full[s]), use & 1, 3) || !wait(smem_u32(&conv_full[s]), use & 1, 3)) {
                         ok = false;
                         break;
                     }
@@ -276,6 +300,9 @@ __global__ void __launch_bounds__(THREADS, 1) qlinear_prefill_kn_kernel(const __
                 }
                 if (ok) umma_commit(smem_u32(&acc_full[buf]));
             }
+            // Teardown: no MMA may still be running when the tensor memory is given back.
+            umma_commit(smem_u32(&drain_bar));
+            if (!mbar_wait(smem_u32(&drain_bar), 0)) report_timeout(p.status, kKernelPrefill, 8);
         }
     } else if (warp >= CONV_WARP0 && warp < CONV_WARP0 + CONV_WARPS) {
         // ---------------- converters ----------------
@@ -300,9 +327,7 @@ __global__ void __launch_bounds__(THREADS, 1) qlinear_prefill_kn_kernel(const __
                 const uint32_t use = i / STAGES;
                 // The int8 tile must have landed (on the barrier of this slot that belongs to this group),
                 // and the MMAs that read the f16 slot last time must be done.
-                if (!mbar_wait(smem_u32(&raw_full[r][group]), (i / RAW_PERIOD) & 1) ||
-                    (use >= 1 && !mbar_wait(smem_u32(&slot_free[s]), (use - 1) & 1))) {
-                    report_timeout(p.status, kKernelPrefill, 4);
+                if (!wait(smem_u32(&raw_full[r][group]), (i / RAW_PERIOD) & 1, 4) || (use >= 1 && !wait(smem_u32(&slot_free[s]), (use - 1) & 1, 4))) {
                     ok = false;
                     break;
                 }
@@ -369,10 +394,7 @@ __global__ void __launch_bounds__(THREADS, 1) qlinear_prefill_kn_kernel(const __
             const int n0 = (tile % p.n_tiles) * TN;
             const int m0 = (tile / p.n_tiles) * TM;
             const uint32_t buf = t_iter & 1, acc_use = t_iter >> 1;
-            if (!mbar_wait(smem_u32(&acc_full[buf]), acc_use & 1)) {
-                report_timeout(p.status, kKernelPrefill, 5);
-                break;
-            }
+            if (!wait(smem_u32(&acc_full[buf]), acc_use & 1, 5)) break;
             tc_fence_after_sync();
             const int n = n0 + 32 * q + lane;
             const float sc = n < p.N ? __half2float(p.scale[n]) : 0.0f;

@@ -27,12 +27,24 @@ def hidet_b200_backend(gm: fx.GraphModule, example_inputs: List[Any], options: O
     return gm.forward
 
 
+def hidet_backend(gm: fx.GraphModule, example_inputs: List[Any], options: Optional[Dict[str, Any]] = None, **kwargs):
+    """The same backend under the reference's own name.  Like the reference's, it quantizes nothing unless asked:
+    torch.compile(model, backend='hidet', options={'precision': 'int8'})."""
+    options = dict(options or {})
+    options.update(kwargs.pop('options', None) or {})
+    options.setdefault('precision', None)
+    return hidet_b200_backend(gm, example_inputs, options=options)
+
+
 def register() -> None:
-    """Makes backend='hidet_b200' known to torch.compile (idempotent)."""
+    """Makes backend='hidet_b200' known to torch.compile and, where no package has claimed the reference's
+    backend name, backend='hidet' as well, so that code written for the reference keeps working (idempotent)."""
     global _registered
     if _registered:
         return
-    from torch._dynamo import register_backend
+    from torch._dynamo import list_backends, register_backend
 
     register_backend(name='hidet_b200', compiler_fn=hidet_b200_backend)
+    if 'hidet' not in list_backends(exclude_tags=()):
+        register_backend(name='hidet', compiler_fn=hidet_backend)
     _registered = True

@@ -22,7 +22,7 @@ import torch.nn.functional as F
 
 from .. import quant
 from .operators import SymmetricDeQuantizationOp, SymmetricQuantizedMatmulOp
-from .transforms import SubgraphRewriteRule
+from .transforms import SubgraphRewriteRule, drop_unused_constants
 
 
 def _fusable(k: int, n: int) -> bool:
@@ -334,7 +334,7 @@ class QuantizedLinearEpilogueFusion(SubgraphRewriteRule):
                 break
         # weights that only the unfused calls used
         if count:
-            gm.graph.eliminate_dead_code()
+            drop_unused_constants(gm)
             used = {n.target for n in gm.graph.nodes if n.op == 'get_attr'}
             for name in list(buffers):
                 if name.startswith('_b200q_') and name not in used and hasattr(gm, name):
@@ -376,8 +376,13 @@ class SymmetricEmbeddingQuantizePattern(SubgraphRewriteRule):
                     table, ind = mod.weight.detach(), node.args[0]
             elif node.op == 'call_function' and node.target is F.embedding:
                 w = node.args[1] if len(node.args) > 1 else node.kwargs.get('weight')
-                plain = all(node.kwargs.get(k) in (None, False, 2.0) for k in ('padding_idx', 'max_norm', 'norm_type', 'scale_grad_by_freq', 'sparse'))
-                if isinstance(w, fx.Node) and w.name in constants and len(node.args) <= 2 and plain:
+                # padding_idx, max_norm, norm_type, scale_grad_by_freq, sparse: only their defaults (a padding index
+                # changes nothing in the forward pass either)
+                extras = list(node.args[2:]) + [node.kwargs.get(k) for k in ('max_norm', 'norm_type', 'scale_grad_by_freq', 'sparse')]
+                plain = all(v in (None, False, 2.0, -1) or (i == 0 and isinstance(v, int)) for i, v in enumerate(extras))
+                if len(node.args) > 3 and node.args[3] is not None:
+                    plain = False  # max_norm renormalises the table
+                if isinstance(w, fx.Node) and w.name in constants and plain:
                     table, ind = constants[w.name], node.args[0]
             if table is None or table.dim() != 2 or not table.is_cuda or table.dtype not in (torch.float16, torch.bfloat16, torch.float32):
                 continue

@@ -150,13 +150,21 @@ def module_constants(gm: fx.GraphModule, example_inputs=None) -> Dict[str, torch
     return consts
 
 
+def drop_unused_constants(gm: fx.GraphModule) -> None:
+    """Removes get_attr nodes that lost their last user.  (Not fx's dead-code elimination: that also drops
+    in-place updates whose result nobody reads, such as writes into a key/value cache.)"""
+    for node in list(gm.graph.nodes):
+        if node.op == 'get_attr' and not node.users:
+            gm.graph.erase_node(node)
+
+
 def selective_quantize_pass(gm: fx.GraphModule, constants: Dict[str, torch.Tensor]) -> int:
     """Applies the context's quantize patterns (python/hidet/graph/transforms/selective_quantize.py:20-24)."""
     total = 0
     for rule in PassContext.current().configs['quantize_patterns']:
         total += rule.apply(gm, constants)
     if total:
-        gm.graph.eliminate_dead_code()
+        drop_unused_constants(gm)
         gm.graph.lint()
         gm.recompile()
     return total

@@ -36,6 +36,9 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 ROOT = os.path.dirname(HERE)
 OUT = os.path.join(HERE, '_ref')
 
+INCLUDE_DIR = os.path.join(ROOT, 'include')
+LIBRARY_DIR = os.path.join(ROOT, 'hidet_b200', 'lib')
+
 RUNTIME_SOURCES = [
     'src/hidet/runtime/cuda/context.cpp', 'src/hidet/runtime/cuda/cublas.cpp', 'src/hidet/runtime/cuda/cudnn.cpp',
     'src/hidet/runtime/cuda/cuda.cpp', 'src/hidet/runtime/hip/context.cpp', 'src/hidet/runtime/cpu/context.cpp',
@@ -66,7 +69,14 @@ CASES = [
     ('quant_bf16_d0_4096x4096', 'quantize', {'rows': 4096, 'cols': 4096, 'dims': 0, 'wtype': 'bfloat16'}),
     ('dequant_f16_i16_d0_200x48', 'dequantize', {'rows': 200, 'cols': 48, 'dims': 0, 'qtype': 'int16'}),
     ('dequant_bf16_d0_200x48', 'dequantize', {'rows': 200, 'cols': 48, 'dims': 0, 'wtype': 'bfloat16'}),
+    # The drop-in itself: a task of the reference whose CUDA implementation is a `launch` that calls this
+    # repository's library (b200q_task below), generated, compiled and linked the reference's way.
+    ('b200q_task_4x4096x4096', 'b200q_task', {'m': 4, 'k': 4096, 'n': 4096}),
+    ('b200q_task_16x8192x1024', 'b200q_task', {'m': 16, 'k': 8192, 'n': 1024}),
+    ('b200q_task_300x1024x768', 'b200q_task', {'m': 300, 'k': 1024, 'n': 768}),
+    ('b200q_task_3x100x36', 'b200q_task', {'m': 3, 'k': 100, 'n': 36}),
 ]
+
 
 
 def reference_root() -> str:
@@ -101,6 +111,7 @@ def generate_sources(ref: str, scratch: str) -> dict:
     """Imports the reference from the scratch copy and lets it write the CUDA source of every case."""
     os.environ['HIDET_REFERENCE'] = ref
     sys.path.insert(0, os.path.join(ROOT, 'tests', 'golden'))
+    sys.path.insert(0, HERE)
     import gen_reference_cpu as helper   # scratch copy of the package, stand-ins for packages this image lacks
 
     helper.REFERENCE = ref
@@ -125,6 +136,11 @@ def generate_sources(ref: str, scratch: str) -> dict:
         elif kind == 'dequantize':
             scale_len = p['cols'] if p['dims'] == 0 else p['rows']
             task = SymmetricDeQuantizationTask(tensor_input('wq', qtype, [p['rows'], p['cols']]), tensor_input('scale', wtype, [scale_len]), dims=p['dims'])
+        elif kind == 'b200q_task':
+            import b200q_binding
+
+            task = b200q_binding.b200q_task(hidet, tensor_input('a', 'float16', [p['m'], p['k']]), tensor_input('b', 'int8', [p['k'], p['n']]),
+                              tensor_input('scale', 'float16', [p['n']]))
         elif kind == 'matmul_f16_i8':
             task = SymmetricQuantizedMatmulF16I8Task(tensor_input('a', 'float16', [p['m'], p['k']]), tensor_input('b', 'int8', [p['k'], p['n']]),
                                                      tensor_input('scale', 'float16', [p['n']]), 1)
@@ -142,8 +158,11 @@ def generate_sources(ref: str, scratch: str) -> dict:
     return sources
 
 
-def compile_case(ref: str, src: str, out: str) -> None:
-    cmd = ['nvcc', '-I' + os.path.join(ref, 'include'), '-L' + OUT, '-O3', '-Xcompiler', '-fPIC,-m64,-O3,-funroll-loops,-ffast-math', '-std=c++11',
+def compile_case(ref: str, src: str, out: str, binding: bool = False) -> None:
+    extra = []
+    if binding:  # what the reference's build adds for ir_module.include_dirs / linking_dirs / linking_libs
+        extra = ['-I' + INCLUDE_DIR, '-L' + LIBRARY_DIR, '-l:libhidet_b200q.so', '-Xlinker', '-rpath,$ORIGIN/../../hidet_b200/lib']
+    cmd = ['nvcc', *extra, '-I' + os.path.join(ref, 'include'), '-L' + OUT, '-O3', '-Xcompiler', '-fPIC,-m64,-O3,-funroll-loops,-ffast-math', '-std=c++11',
            '-gencode', 'arch=compute_100a,code=sm_100a', '-lineinfo', '-ftz=true', '-prec-div=false', '-lhidet_runtime', '--cudart', 'shared',
            '--diag-suppress', '177', '--diag-suppress', '179', '--diag-suppress', '39', '-Xlinker', '-rpath,$ORIGIN', '--shared', src, '-o', out]
     subprocess.check_call(cmd, stdout=subprocess.DEVNULL)
@@ -169,7 +188,9 @@ def build(scratch: str = '', force: bool = False) -> bool:
     sources = json.load(open(listing))
     cases = []
     for name, kind, p in CASES:
-        compile_case(ref, sources[name], os.path.join(OUT, name + '.so'))
+        compile_case(ref, sources[name], os.path.join(OUT, name + '.so'), binding=(kind == 'b200q_task'))
+        if kind == 'b200q_task' and name == 'b200q_task_4x4096x4096':
+            shutil.copy(sources[name], os.path.join(OUT, 'b200q_task_source.cu.txt'))   # quoted in the integration notes
         cases.append({'name': name, 'kind': kind, 'file': name + '.so', **p})
     json.dump({'digest': digest, 'runtime': 'libhidet_runtime.so', 'cases': cases}, open(manifest_path, 'w'), indent=1)
     return True

@@ -66,15 +66,19 @@ class ReferenceKernels:
 
     def launch(self, name: str, *tensors) -> None:
         """hidet_launch of one case on torch's current stream; raises with the reference's own message."""
+        for t in tensors:
+            assert t.is_cuda and t.is_contiguous()
+        self.launch_pointers(name, *[t.data_ptr() for t in tensors])
+
+    def launch_pointers(self, name: str, *pointers) -> None:
+        """The same with raw device addresses (0 for a null pointer)."""
         torch = self.torch
         lib = self._libs.get(name)
         if lib is None:
             lib = self._libs[name] = ctypes.CDLL(os.path.join(REF_DIR, self.cases[name]['file']))
             lib.hidet_launch.restype = None
-        for t in tensors:
-            assert t.is_cuda and t.is_contiguous()
         self.runtime.set_cuda_stream(ctypes.c_void_p(torch.cuda.current_stream().cuda_stream))
-        lib.hidet_launch(*[ctypes.c_void_p(t.data_ptr()) for t in tensors])
+        lib.hidet_launch(*[ctypes.c_void_p(p) for p in pointers])
         err = self.runtime.hidet_get_last_error()
         if err:
             raise RuntimeError('reference kernel {}: {}'.format(name, err.decode()))

@@ -32,6 +32,7 @@ class PipelineConfig:
     group_warps: int
     raw_period: int      # stages after which a (slot, group) pair recurs
     per_group_barriers: bool = True   # one "landed" barrier per (slot, group); False = one per slot
+    drain_on_exit: bool = True        # producer / MMA lane wait for what they have in flight before the CTA retires
 
 
 def _ternary(text: str, name: str, tm: int) -> int:
@@ -87,6 +88,10 @@ class Barrier:
 Wait = Optional[Callable[[], bool]]
 
 
+class Aborted(Exception):
+    """Raised inside a role when the CTA-wide abort flag ends one of its waits."""
+
+
 class Pipeline:
     def __init__(self, cfg: PipelineConfig, tiles: int, k_blocks: int, rng: random.Random):
         self.cfg, self.tiles, self.k_blocks, self.rng = cfg, tiles, k_blocks, rng
@@ -110,9 +115,21 @@ class Pipeline:
         self.copies: List[Callable[[], None]] = []      # copies in flight: may land in any order
         self.commits: List[Callable[[], None]] = []     # tensor-core commits: land in order
         self.mma_reading: Dict[int, int] = {}           # stage slot -> stage index the tensor core still reads
+        self.abort = False                              # the CTA-wide flag a role raises when its own wait runs out
+        self.expire: Optional[Tuple[int, int]] = None   # (agent, n): that agent's n-th blocked wait "runs out"
+        self.retired_dirty: Optional[str] = None
 
     # ---- roles ----
     def producer(self) -> Generator[Wait, None, None]:
+        try:
+            yield from self._producer_loop()
+        except Aborted:
+            pass
+        if self.cfg.drain_on_exit:
+            # teardown: every copy armed by this lane must have landed (copies land without anyone's help)
+            yield ('drain', lambda: not self.copies)
+
+    def _producer_loop(self) -> Generator[Wait, None, None]:
         c = self.cfg
         i = 0
         for _tile in range(self.tiles):
@@ -145,6 +162,12 @@ class Pipeline:
                 i += 1
 
     def converter(self, group: int, warp: int) -> Generator[Wait, None, None]:
+        try:
+            yield from self._converter_loop(group, warp)
+        except Aborted:
+            pass
+
+    def _converter_loop(self, group: int, warp: int) -> Generator[Wait, None, None]:
         c = self.cfg
         for i in range(self.tiles * self.k_blocks):
             if i % c.conv_groups != group:
@@ -167,6 +190,15 @@ class Pipeline:
             yield None
 
     def mma(self) -> Generator[Wait, None, None]:
+        try:
+            yield from self._mma_loop()
+        except Aborted:
+            pass
+        if self.cfg.drain_on_exit:
+            # teardown: a final commit; it arrives when every MMA issued so far has completed
+            yield ('drain', lambda: not self.commits)
+
+    def _mma_loop(self) -> Generator[Wait, None, None]:
         c = self.cfg
         i = 0
         for t in range(self.tiles):
@@ -201,7 +233,13 @@ class Pipeline:
             self.commits.append(finished)
             yield None
 
-    def epilogue(self, _warp: int) -> Generator[Wait, None, None]:
+    def epilogue(self, warp: int) -> Generator[Wait, None, None]:
+        try:
+            yield from self._epilogue_loop(warp)
+        except Aborted:
+            pass
+
+    def _epilogue_loop(self, _warp: int) -> Generator[Wait, None, None]:
         for t in range(self.tiles):
             buf, acc_use = t & 1, t >> 1
             yield lambda buf=buf, p=acc_use & 1: self.acc_full[buf].test(p)
@@ -221,14 +259,37 @@ class Pipeline:
         agents: List[Generator[Wait, None, None]] = [self.producer(), self.mma()]
         agents += [self.converter(g, w) for g in range(c.conv_groups) for w in range(c.group_warps)]
         agents += [self.epilogue(w) for w in range(4)]
-        waits: List[Wait] = [None] * len(agents)
+        waits: List = [None] * len(agents)
         alive = [True] * len(agents)
+        blocked_count = [0] * len(agents)
         steps = 0
+
+        def ready(k: int) -> bool:
+            w = waits[k]
+            if w is None:
+                return True
+            if isinstance(w, tuple):          # a teardown wait: not cut short by the abort flag
+                return w[1]()
+            if w():
+                return True
+            if self.abort:
+                return True                   # the wait ends; the role sees the flag and leaves
+            return False
+
         while any(alive) or self.copies or self.commits:
             steps += 1
             if steps > max_steps:
                 raise ProtocolError('no end after {} steps'.format(max_steps))
-            runnable = [k for k in range(len(agents)) if alive[k] and (waits[k] is None or waits[k]())]
+            if not any(alive) and (self.copies or self.commits) and self.retired_dirty is None:
+                self.retired_dirty = '{} copies and {} commits in flight'.format(len(self.copies), len(self.commits))
+            # a blocked wait of the chosen agent "runs out": that role raises the flag
+            if self.expire is not None and not self.abort:
+                k, n = self.expire
+                if alive[k] and waits[k] is not None and not isinstance(waits[k], tuple) and not waits[k]():
+                    blocked_count[k] += 1
+                    if blocked_count[k] >= n:
+                        self.abort = True
+            runnable = [k for k in range(len(agents)) if alive[k] and ready(k)]
             choices: List[Tuple[str, int]] = [('agent', k) for k in runnable]
             if self.commits:
                 choices.append(('commit', 0))
@@ -244,7 +305,13 @@ class Pipeline:
                 self.commits.pop(0)()
             else:
                 try:
-                    waits[k] = next(agents[k])
+                    w = waits[k]
+                    if w is not None and not isinstance(w, tuple) and self.abort and not w():
+                        waits[k] = agents[k].throw(Aborted())   # the wait ended because of the flag
+                    else:
+                        waits[k] = next(agents[k])
                 except StopIteration:
                     alive[k] = False
+        if self.retired_dirty is not None:
+            raise ProtocolError('the CTA retired with ' + self.retired_dirty)
         return steps

@@ -258,3 +258,9 @@ def test_torch_compile_backend_quantizes_a_decoder_block():
     assert (got.float() - want.float()).abs().max() < 5e-2
     # the weights really went through the quantized kernels: int8 codes differ from fp16 weights' output
     assert not torch.equal(got, want)
+    # the reference's own backend name works too, and like the reference's it quantizes only when asked
+    with torch.no_grad():
+        as_hidet = torch.compile(model, backend='hidet', options={'precision': 'int8'})(x)
+        plain = torch.compile(model, backend='hidet')(x)
+    assert torch.equal(as_hidet, got)
+    assert (plain.float() - want.float()).abs().max() < 2e-3

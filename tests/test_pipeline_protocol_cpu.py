@@ -48,3 +48,36 @@ def test_shared_barrier_is_fine_when_every_slot_keeps_its_group():
     assert cfg.raw_slots % cfg.conv_groups == 0
     for seed in range(30):
         Pipeline(cfg, 3, 16, random.Random(seed)).run(copy_delay=0.9)
+
+
+@pytest.mark.parametrize('tm', [256, 64])
+def test_a_wait_that_runs_out_ends_every_role_and_the_cta_retires_clean(tm):
+    """Any role's wait may run out at any time (modelled: the n-th time the scheduler finds that role blocked).  The
+    role raises the CTA-wide flag, every other wait ends on it, the producer waits for the copies it armed and the
+    MMA lane for a final commit: when the last role is gone nothing is in flight, so nothing writes to shared
+    memory or reads tensor memory of a CTA that has retired."""
+    cfg = config_from_source(tm)
+    n_agents = 2 + 8 + 4
+    runs = 0
+    for seed in range(25):
+        for agent in range(n_agents):
+            for nth in (1, 3, 17):
+                pipe = Pipeline(cfg, 3, 9, random.Random(seed))
+                pipe.expire = (agent, nth)
+                pipe.run(copy_delay=0.9)
+                runs += 1 if pipe.abort else 0
+    assert runs > 100   # the flag was really raised in most of these schedules
+
+
+def test_model_catches_a_teardown_without_the_drain():
+    cfg = dataclasses.replace(config_from_source(256), drain_on_exit=False)
+    failures = 0
+    for seed in range(40):
+        pipe = Pipeline(cfg, 3, 9, random.Random(seed))
+        pipe.expire = (1, 2)   # the MMA lane gives up early: copies and commits are still in flight
+        try:
+            pipe.run(copy_delay=0.95)
+        except ProtocolError as e:
+            assert 'retired with' in str(e)
+            failures += 1
+    assert failures > 0

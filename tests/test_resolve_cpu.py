@@ -40,3 +40,34 @@ def test_pass_context_precision_switch():
         SymmetricLinearQuantizePattern(quant_type='int16')
     with pytest.raises(ValueError):
         SymmetricLinearQuantizePattern(dims=-1)
+
+
+def test_the_pass_keeps_in_place_updates_nobody_reads():
+    """A decoder writes keys and values into its cache in place and reads the cache, not the write's result; the
+    clean-up after a rewrite must not take such writes for dead code."""
+    import torch
+    import torch.fx as fx
+
+    from hidet_b200.graph.transforms import SubgraphRewriteRule, optimize
+
+    class WritesCache(torch.nn.Module):
+        def __init__(self):
+            super().__init__()
+            self.register_buffer('unused', torch.ones(3))
+
+        def forward(self, cache, pos, x):
+            cache.index_copy_(0, pos, x)
+            return cache.sum() + self.unused.sum() * 0
+
+    class CountsOne(SubgraphRewriteRule):
+        def apply(self, gm, constants):
+            return 1
+
+    gm = fx.symbolic_trace(WritesCache())
+    with PassContext() as ctx:
+        ctx.add_quantize_rules([CountsOne()])
+        optimize(gm)
+    assert any(n.op == 'call_method' and n.target == 'index_copy_' for n in gm.graph.nodes)
+    cache = torch.zeros(4, 2)
+    out = gm(cache, torch.tensor([1]), torch.full((1, 2), 3.0))
+    assert float(out) == 6.0 and float(cache[1, 0]) == 3.0
