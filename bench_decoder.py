@@ -10,7 +10,7 @@ weights and token ids are seeded random numbers of the same shapes.
 The model keeps a static key/value cache and is called in two shapes only (the prompt pass and the one-token
 step), so there is one compiled graph per shape and the step is replayed as a CUDA graph (hidet_b200.CudaGraph).
 `run_config` returns prompt time, time per decode step and the parity of the compiled int8 model's logits with the
-same decoder run eagerly on dequantized weights (teacher-forced with the eager arm's tokens).
+same decoder run eagerly in fp32 on dequantized weights (teacher-forced with that arm's tokens).
 
 Used by bench.py (`--config4`, and as the `config4` block of the default line) and by tests/test_decoder_gpu.py.
 """
@@ -135,11 +135,11 @@ def with_dequantized_weights(model: Decoder) -> Decoder:
     return ref
 
 
-def greedy(model, cfg: DecoderConfig, prompt, steps: int, forced=None):
+def greedy(model, cfg: DecoderConfig, prompt, steps: int, forced=None, dtype=torch.float16):
     """Prompt pass, then `steps` one-token passes, eagerly (no CUDA graph).  Feeds its own greedy tokens, or
     `forced` ones.  Returns (logits of every pass [steps + 1, vocab], tokens)."""
     device = prompt.device
-    kc, vc = empty_caches(cfg, device)
+    kc, vc = empty_caches(cfg, device, dtype)
     logits = model(prompt, kc, vc, torch.arange(cfg.prompt, device=device))
     all_logits, tokens = [logits], []
     for step in range(steps):
@@ -166,10 +166,15 @@ def run_config(cfg: DecoderConfig = LLAMA_7B, parity_steps: int = 8, seed: int =
     out = {'model': {'layers': cfg.layers, 'hidden': cfg.hidden, 'heads': cfg.heads, 'ffn': cfg.ffn, 'vocab': cfg.vocab},
            'prompt_tokens': cfg.prompt, 'decode_steps': cfg.steps, 'batch': 1}
     with torch.no_grad():
-        # ---- parity: teacher-forced with the eager arm's own greedy tokens ----
-        ref = with_dequantized_weights(model)
-        ref_logits, ref_tokens = greedy(ref, cfg, prompt, parity_steps)
-        del ref
+        # ---- parity: all arms see the tokens the fp32 arm chooses greedily ----
+        # The oracle is the same decoder on dequantized weights in fp32 (no rounding between layers); beside it,
+        # the error of the eager fp16 decoder on the same weights shows what fp16 rounding alone costs.
+        ref16 = with_dequantized_weights(model)
+        ref32 = copy.deepcopy(ref16).float()
+        ref_logits, ref_tokens = greedy(ref32, cfg, prompt, parity_steps, dtype=torch.float32)
+        del ref32
+        eager_logits, _ = greedy(ref16, cfg, prompt, parity_steps, forced=ref_tokens)
+        del ref16
         torch.cuda.empty_cache()
         t0 = time.perf_counter()
         compiled = torch.compile(model, backend='hidet_b200', options={'precision': 'int8'}, dynamic=False)
@@ -177,7 +182,9 @@ def run_config(cfg: DecoderConfig = LLAMA_7B, parity_steps: int = 8, seed: int =
         torch.cuda.synchronize()
         out['compile_and_first_passes_s'] = round(time.perf_counter() - t0, 1)
         top = ref_logits.abs().max().item()
-        out['parity'] = {'passes_compared': parity_steps + 1, 'max_abs_err_over_max_ref': (got_logits - ref_logits).abs().max().item() / top,
+        out['parity'] = {'against': 'the decoder on dequantized weights in fp32, teacher-forced', 'passes_compared': parity_steps + 1,
+                         'max_abs_err_over_max_ref': (got_logits - ref_logits).abs().max().item() / top,
+                         'eager_f16_max_abs_err_over_max_ref': (eager_logits - ref_logits).abs().max().item() / top,
                          'argmax_agreement': (got_logits.argmax(-1) == ref_logits.argmax(-1)).float().mean().item()}
 
         # ---- timing ----

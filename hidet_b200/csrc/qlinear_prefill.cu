@@ -151,6 +151,19 @@ struct Params {
 // FUSED: the epilogue of p.ep (bias, gate / up pairing, residual) is compiled in.
 // NK: the weight is [N, K] with K contiguous: the int8 tile is 128 weight rows of 64 k-bytes and its f16
 //     image is the K-major MMA operand (rows of 128 bytes, 128B swizzle), like the activation tile.
+constexpr uint32_t kFastPolls = 4096;
+// The rest of a bounded wait: polls on, looking at the CTA's abort flag between runs of polls; when its own
+// limit runs out it records the site and raises the flag for the other roles.
+__device__ __noinline__ bool wait_or_abort(uint32_t bar, uint32_t parity, unsigned int site, int *abort_flag, unsigned int *status) {
+    for (uint32_t round = 0; round < kSpinLimit / 1024u; ++round) {
+        if (mbar_wait(bar, parity, 1024u)) return true;
+        if (*reinterpret_cast<volatile int *>(abort_flag) != 0) return false;
+    }
+    report_timeout(status, kKernelPrefill, site);
+    atomicExch(abort_flag, 1);
+    return false;
+}
+
 template <int TM, bool FUSED, bool NK>
 __global__ void __launch_bounds__(THREADS, 1) qlinear_prefill_kn_kernel(const __grid_constant__ CUtensorMap map_w,
                                                                         const __grid_constant__ CUtensorMap map_a,
@@ -214,14 +227,12 @@ __global__ void __launch_bounds__(THREADS, 1) qlinear_prefill_kn_kernel(const __
     tc_fence_after_sync();
     const uint32_t tmem_base = tmem_base_slot;
     // Bounded wait that also ends when another role has given up; the role whose own limit runs out reports it.
+    // The first polls are the plain inlined loop; everything else lives in a function of its own, so that the
+    // code around the hot loops stays what it is without the flag (with the flag test inlined at every wait the
+    // kernel lost a tenth of its speed, although the test never ran).
     auto wait = [&](uint32_t bar, uint32_t parity, unsigned int site) -> bool {
-        for (uint32_t i = 0; i < kSpinLimit; ++i) {
-            if (mbar_try_wait(bar, parity)) return true;
-            if (*reinterpret_cast<volatile int *>(&abort_flag) != 0) return false;
-        }
-        report_timeout(p.status, kKernelPrefill, site);
-        atomicExch(&abort_flag, 1);
-        return false;
+        if (mbar_wait(bar, parity, kFastPolls)) return true;
+        return wait_or_abort(bar, parity, site, &abort_flag, p.status);
     };
 
     if (warp == PRODUCER_WARP) {
@@ -232,9 +243,7 @@ __global__ void __launch_bounds__(THREADS, 1) qlinear_prefill_kn_kernel(const __
             const uint64_t keep = l2_policy_evict_last();  // both operands are re-read by other tiles: keep them in L2
             uint32_t i = 0;
             bool ok = true;
-            int last_raw[RAW_SLOTS], last_act[STAGES];  // the latest stage copied into each slot (-1: none)
-            for (int r = 0; r < RAW_SLOTS; ++r) last_raw[r] = -1;
-            for (int s = 0; s < STAGES; ++s) last_act[s] = -1;
+            uint32_t n_raw = 0, n_act = 0;  // copies armed so far (stages 0 .. n - 1), for the teardown
             for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
                 const int n0 = (tile % p.n_tiles) * TN;
                 const int m0 = (tile / p.n_tiles) * TM;
@@ -248,7 +257,7 @@ __global__ void __launch_bounds__(THREADS, 1) qlinear_prefill_kn_kernel(const __
                     const uint32_t raw_bar = smem_u32(&raw_full[r][i % CONV_GROUPS]);  // the group that converts stage i
                     mbar_expect_tx(raw_bar, RAW_BYTES);
                     tma_load_2d_hint(raw_addr(r), &map_w, NK ? kb * BK : n0, NK ? n0 : kb * BK, raw_bar, keep);
-                    last_raw[r] = (int)i;
+                    n_raw = i + 1;
                     const int s = i % STAGES;
                     const uint32_t use = i / STAGES;
                     if (use >= 1 && !wait(smem_u32(&slot_free[s]), (use - 1) & 1, 6)) {
@@ -257,17 +266,22 @@ __global__ void __launch_bounds__(THREADS, 1) qlinear_prefill_kn_kernel(const __
                     }
                     mbar_expect_tx(smem_u32(&act_full[s]), Cfg::ACT_BYTES);
                     tma_load_2d_hint(act_addr(s), &map_a, kb * BK, m0, smem_u32(&act_full[s]), keep);
-                    last_act[s] = (int)i;
+                    n_act = i + 1;
                 }
             }
             // Teardown: every copy this lane has armed must have landed before the CTA may retire.  After a
             // normal run they all have (their stages were consumed); after an abort this waits for the stragglers.
-            for (int r = 0; r < RAW_SLOTS; ++r)
-                if (last_raw[r] >= 0 && !mbar_wait(smem_u32(&raw_full[r][last_raw[r] % CONV_GROUPS]), (uint32_t)(last_raw[r] / RAW_PERIOD) & 1))
-                    report_timeout(p.status, kKernelPrefill, 7);
-            for (int s = 0; s < STAGES; ++s)
-                if (last_act[s] >= 0 && !mbar_wait(smem_u32(&act_full[s]), (uint32_t)(last_act[s] / STAGES) & 1))
-                    report_timeout(p.status, kKernelPrefill, 7);
+            // The latest stage copied into slot x of a ring of n slots, of c copies: the largest j < c with j % n == x.
+            for (uint32_t r = 0; r < (uint32_t)RAW_SLOTS; ++r) {
+                if (n_raw <= r) continue;
+                const uint32_t j = n_raw - 1 - (n_raw - 1 - r) % RAW_SLOTS;
+                if (!mbar_wait(smem_u32(&raw_full[r][j % CONV_GROUPS]), (j / RAW_PERIOD) & 1)) report_timeout(p.status, kKernelPrefill, 7);
+            }
+            for (uint32_t s = 0; s < (uint32_t)STAGES; ++s) {
+                if (n_act <= s) continue;
+                const uint32_t j = n_act - 1 - (n_act - 1 - s) % STAGES;
+                if (!mbar_wait(smem_u32(&act_full[s]), (j / STAGES) & 1)) report_timeout(p.status, kKernelPrefill, 7);
+            }
         }
     } else if (warp == MMA_WARP) {
         // ---------------- MMA issuer ----------------

@@ -22,7 +22,7 @@ import torch.nn.functional as F
 
 from .. import quant
 from .operators import SymmetricDeQuantizationOp, SymmetricQuantizedMatmulOp
-from .transforms import SubgraphRewriteRule, drop_unused_constants
+from .transforms import PURE_TARGETS, SubgraphRewriteRule, drop_unused_constants
 
 
 def _fusable(k: int, n: int) -> bool:
@@ -393,6 +393,9 @@ class SymmetricEmbeddingQuantizePattern(SubgraphRewriteRule):
             gm.graph.erase_node(node)
             count += 1
         return count
+
+
+PURE_TARGETS.update({quantized_linear_nk, quantized_matmul, dequantized_weight, quantized_embedding})
 
 
 def symmetric_linear_patterns(quant_type: str = 'int8', dims: Union[int, List[int]] = 0) -> List[SubgraphRewriteRule]:

@@ -150,11 +150,17 @@ def module_constants(gm: fx.GraphModule, example_inputs=None) -> Dict[str, torch
     return consts
 
 
+PURE_TARGETS = set()   # functions the rewrite rules insert that have no side effect (filled by the rules' module)
+
+
 def drop_unused_constants(gm: fx.GraphModule) -> None:
-    """Removes get_attr nodes that lost their last user.  (Not fx's dead-code elimination: that also drops
-    in-place updates whose result nobody reads, such as writes into a key/value cache.)"""
-    for node in list(gm.graph.nodes):
-        if node.op == 'get_attr' and not node.users:
+    """Removes what a rewrite left without users: get_attr nodes and calls of the rules' own side-effect-free
+    functions.  (Not fx's dead-code elimination: that also drops in-place updates whose result nobody reads, such
+    as writes into a key/value cache.)"""
+    for node in reversed(list(gm.graph.nodes)):
+        if node.users:
+            continue
+        if node.op == 'get_attr' or (node.op == 'call_function' and node.target in PURE_TARGETS):
             gm.graph.erase_node(node)
 
 

@@ -44,7 +44,7 @@ def test_compiled_int8_decoder_follows_the_eager_decoder_on_dequantized_weights(
 
 def test_small_configuration_through_the_benchmark_driver():
     out = bench_decoder.run_config(bench_decoder.SMALL, parity_steps=6)
-    assert out['parity']['max_abs_err_over_max_ref'] <= 1e-2 and out['parity']['argmax_agreement'] >= 0.85
+    assert out['parity']['max_abs_err_over_max_ref'] <= 1e-2 and out['parity']['argmax_agreement'] >= 0.85, out['parity']
     assert out['generated_tokens'] == bench_decoder.SMALL.steps and out['ms_per_decode_step'] > 0
 
 
@@ -55,6 +55,7 @@ def test_llama_7b_shaped_decoder_at_full_size():
         pytest.skip('needs about 45 GB of device memory')
     cfg = bench_decoder.DecoderConfig(steps=16)   # the full model; fewer steps than the benchmark's 128
     out = bench_decoder.run_config(cfg, parity_steps=8)
-    assert out['parity']['max_abs_err_over_max_ref'] <= 1e-2
-    assert out['parity']['argmax_agreement'] >= 0.75   # 9 passes over random weights: near-ties are common
+    # the oracle is the fp32 decoder on dequantized weights; the eager fp16 decoder's own distance from it is reported beside
+    assert out['parity']['max_abs_err_over_max_ref'] <= 1e-2, out['parity']
+    assert out['parity']['argmax_agreement'] >= 0.75, out['parity']   # 9 passes over random weights: near-ties are common
     assert out['generated_tokens'] == 16 and out['prompt_ms'] > 0 and out['ms_per_decode_step'] > 0

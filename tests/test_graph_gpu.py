@@ -264,3 +264,29 @@ def test_torch_compile_backend_quantizes_a_decoder_block():
         plain = torch.compile(model, backend='hidet')(x)
     assert torch.equal(as_hidet, got)
     assert (plain.float() - want.float()).abs().max() < 2e-3
+
+
+def test_compiled_graph_is_not_reused_with_another_module_s_weights():
+    """torch.compile reuses a compiled graph for any module whose parameters have the same shapes and passes the
+    parameters in as inputs; the quantized copies frozen at rewrite time must follow the module that is called,
+    and weights written in place after compilation must be quantized again."""
+    hg.register()
+
+    def reference(lin, x):
+        wq, scale = hidet_b200.symmetric_quantize(lin.weight.detach().t().contiguous(), 'int8', dims=0)
+        return hidet_b200.symmetric_quant_matmul(x, wq, scale)
+
+    torch.manual_seed(11)
+    first = nn.Linear(256, 384, bias=False).half().cuda().eval()
+    second = nn.Linear(256, 384, bias=False).half().cuda().eval()
+    x = torch.randn(5, 256, device='cuda').half()
+    with torch.no_grad():
+        got_first = torch.compile(first, backend='hidet_b200', options={'precision': 'int8'})(x)
+        compiled_second = torch.compile(second, backend='hidet_b200', options={'precision': 'int8'})
+        got_second = compiled_second(x)
+        assert torch.equal(got_first, reference(first, x))
+        assert torch.equal(got_second, reference(second, x))
+        assert not torch.equal(got_first, got_second)
+        second.weight.mul_(0.5)
+        second.weight[3, :] = 1.0
+        assert torch.equal(compiled_second(x), reference(second, x))
