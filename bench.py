@@ -346,6 +346,32 @@ def extra_sections(torch, hidet_b200, device, stream, peaks):
         one_gpu.append({'M': m, 'K': K_70B, 'N': N_70B, 'us_per_layer_one_gpu': round(us, 2),
                         'GBps': round(algorithmic_bytes(m, K_70B, N_70B) / us / 1e3, 1), 'TFLOPS': round(2.0 * m * K_70B * N_70B / us / 1e6, 1)})
     out['sharded_70b_one_gpu'] = one_gpu
+    del stack
+    # 4-bit weights with group scales and zero points (the shapes and group size of the reference's own test program,
+    # tests/cute_kernel/test_quant_linear.py:53-61): bytes = the packed codes + scales + zero points + activations + output.
+    from hidet_b200.quant import cast_f16_to_u4, w4a16_linear
+
+    w4 = []
+    for m, n, k in ((1, 4096, 4096), (1, 12288, 4096), (1, 4096, 12288)):
+        gsize = 128
+        gen = torch.Generator(device=device).manual_seed(5)
+        count = 12  # 100 to 300 MB of codes in rotation
+        codes = [cast_f16_to_u4(torch.randint(0, 16, (k, n), device=device, generator=gen).to(torch.float16)) for _ in range(count)]
+        scale = (torch.rand(k // gsize, n, device=device, generator=gen) * 0.01).to(torch.float16)
+        zeros = (torch.rand(k // gsize, n, device=device, generator=gen) * 15).to(torch.float16)
+        a = torch.randn(m, k, generator=gen, device=device, dtype=torch.float32).to(torch.float16)
+        linear = w4a16_linear('bench', k, n, gsize, with_zp=True)
+
+        def fn4():
+            for q in codes:
+                linear(a, q, scale, zeros)
+
+        us = time_graph(torch, stream, fn4, count)
+        nbytes = k * n // 2 + 2 * 2 * (k // gsize) * n + 2 * m * k + 2 * m * n
+        w4.append({'M': m, 'K': k, 'N': n, 'group_size': gsize, 'us_per_launch': round(us, 2), 'GBps': round(nbytes / us / 1e3, 1),
+                   'frac_of_hbm_peak': round(nbytes / us / 1e3 / peaks['hbm_gbs'], 4)})
+        del codes
+    out['w4a16'] = w4
     return out
 
 

@@ -2,12 +2,12 @@
 //
 // The op is bound by streaming the int8 weight from HBM once, so the kernel is built around that
 // stream.  A producer warp keeps a ring of TMA tile loads in flight: 64 k-rows x 128 columns of int8,
-// 128B-swizzled, plus the matching 16 x 64 f16 slice of the activations.  Four consumer warps own 32
-// columns each, so no sum ever crosses a warp.  A consumer fetches its slice with transposing matrix
-// loads (four consecutive k of one column per register), turns the bytes into exact f16 pairs in
-// registers and feeds warp-level m16n8k16 tensor-core MMAs with fp32 accumulators; the weight
-// is the MMA's 16-row operand and the activations its 8-column operand, so up to 8 activation rows
-// cost one MMA per 16 x 16 weight block and up to 16 rows two (rows beyond M are zero-filled by TMA).
+// 128B-swizzled, and copies the matching 16 x 64 f16 slice of the activations beside each with
+// cp.async.  Four consumer warps own 32 columns each, so no sum ever crosses a warp.  A consumer
+// fetches its slice with transposing matrix loads (four consecutive k of one column per register),
+// turns the bytes into exact f16 pairs in registers and feeds warp-level m16n8k16 tensor-core MMAs
+// with fp32 accumulators; the weight is the MMA's 16-row operand and the activations its 8-column operand, so up to 8 activation rows
+// cost one MMA per 16 x 16 weight block and up to 16 rows two (rows beyond M are zero-filled).
 //
 // K is split across CTAs to fill the machine.  Up to 8 splits of one output tile form a thread-block
 // cluster: every CTA sends its partial tile into the shared memory of the CTA that owns those columns
@@ -149,6 +149,15 @@ __device__ __forceinline__ float4 lds128f(uint32_t addr) {
 }
 __device__ __forceinline__ void sts32f(uint32_t addr, float v) { asm volatile("st.shared.f32 [%0], %1;" ::"r"(addr), "f"(v) : "memory"); }
 
+// 16 bytes global -> shared without passing through registers; src_bytes = 0 writes zeros instead.
+__device__ __forceinline__ void cp_async_16(uint32_t dst, const void *src, uint32_t src_bytes) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(src_bytes) : "memory");
+}
+// The barrier gets one arrival from this thread once all its earlier cp.async copies have landed.
+__device__ __forceinline__ void cp_async_arrive(uint32_t bar) {
+    asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];" ::"r"(bar) : "memory");
+}
+
 constexpr int kModeDirect = 0;  // one CTA per output tile
 constexpr int kModeSplit = 1;   // `splits` CTAs per tile: clusters of `cluster` CTAs, `groups` clusters per tile
 
@@ -179,6 +188,8 @@ __device__ __forceinline__ void finish(const OutTargets &o, const Epilogue &ep, 
 }
 
 struct Params {
+    const __half *a;          // activations [M, lda]
+    int64_t lda;
     const __half *scale;
     OutTargets out;
     Epilogue ep;
@@ -198,9 +209,7 @@ struct Params {
 //     [K, N]: a stage is then 128 weight rows of 64 k-bytes (64-byte swizzle) and the fragments come from
 //     plain matrix loads; everything else is shared.
 template <int MT, bool NK>
-__global__ void __launch_bounds__(THREADS) qlinear_decode_kn_kernel(const __grid_constant__ CUtensorMap map_w,
-                                                                    const __grid_constant__ CUtensorMap map_a,
-                                                                    const Params p) {
+__global__ void __launch_bounds__(THREADS) qlinear_decode_kn_kernel(const __grid_constant__ CUtensorMap map_w, const Params p) {
     extern __shared__ unsigned char smem_dyn[];
     __shared__ __align__(8) uint64_t full_bar[STAGES];
     __shared__ __align__(8) uint64_t empty_bar[STAGES];
@@ -240,7 +249,7 @@ __global__ void __launch_bounds__(THREADS) qlinear_decode_kn_kernel(const __grid
     if (threadIdx.x == 0) {
 #pragma unroll
         for (int s = 0; s < STAGES; ++s) {
-            mbar_init(smem_u32(&full_bar[s]), 2);  // one arrival for the weight tile, one for the activation tile
+            mbar_init(smem_u32(&full_bar[s]), 1 + 32);  // the weight tile (TMA bytes) and the producer warp's 32 lanes, each when its activation copies have landed
             mbar_init(smem_u32(&empty_bar[s]), CONSUMER_WARPS);
         }
         mbar_init(smem_u32(&recv_bar), 1);
@@ -270,12 +279,36 @@ __global__ void __launch_bounds__(THREADS) qlinear_decode_kn_kernel(const __grid
         for (int mt = 0; mt < MT; ++mt) acc[j][mt][0] = acc[j][mt][1] = acc[j][mt][2] = acc[j][mt][3] = 0.0f;
 
     if (warp == CONSUMER_WARPS) {
-        // ---------------- producer: one lane drives TMA ----------------
+        // ---------------- producer warp ----------------
+        // Lane 0 drives the TMA loads of the weight tiles.  The activation slices (8 MT rows x 64 k of f16 per stage,
+        // 128-byte rows, 16-byte chunk c of row r at chunk c ^ (r & 7), the layout a 128B-swizzled TMA tile would have)
+        // are copied by all 32 lanes with cp.async: they are a few hundred bytes that sit in L2, and on the load/store
+        // path they do not wait in the TMA queue behind weight tiles that are still on their way from HBM.
+        uint32_t dst_off[2 * MT];
+        const __half *src_row[2 * MT];
+        int kc[2 * MT];
+#pragma unroll
+        for (int q = 0; q < 2 * MT; ++q) {
+            const int chunk = lane + 32 * q;  // 8 chunks per row
+            const int r = chunk >> 3, c = chunk & 7;
+            dst_off[q] = r * 128 + ((c ^ (r & 7)) << 4);
+            src_row[q] = m0 + r < p.M ? p.a + (size_t)(m0 + r) * p.lda : nullptr;  // rows beyond M are zero-filled
+            kc[q] = 8 * c;
+        }
+        auto copy_activations = [&](int s, int k0) {
+#pragma unroll
+            for (int q = 0; q < 2 * MT; ++q) {
+                const int k = k0 + kc[q];
+                const bool in = src_row[q] != nullptr && k < p.k_end;  // k_end is a multiple of 8 or the row's end: a chunk is in or out as a whole
+                cp_async_16(a_base + s * A_STAGE_BYTES + dst_off[q], in ? static_cast<const void *>(src_row[q] + k) : static_cast<const void *>(p.a), in ? 16u : 0u);
+            }
+            cp_async_arrive(smem_u32(&full_bar[s]));
+        };
+        const int prologue = n_iters < STAGES ? n_iters : STAGES;
+        uint64_t stream_policy = 0;
         if (lane == 0) {
             tma_prefetch_desc(&map_w);
-            tma_prefetch_desc(&map_a);
-            const uint64_t stream_policy = l2_policy_evict_first();  // the weight is read once
-            const int prologue = n_iters < STAGES ? n_iters : STAGES;
+            stream_policy = l2_policy_evict_first();  // the weight is read once
             // The weight does not depend on the kernel before this one in the stream; the activations
             // may.  Ask for the first weight tiles, then wait for that kernel, then ask for activations.
             for (int it = 0; it < prologue; ++it) {
@@ -283,27 +316,23 @@ __global__ void __launch_bounds__(THREADS) qlinear_decode_kn_kernel(const __grid
                 mbar_expect_tx(bar, W_STAGE_BYTES);
                 tma_load_2d_hint(w_base + it * W_STAGE_BYTES, &map_w, NK ? p.k_begin + (it_begin + it) * BK : n0, NK ? n0 : p.k_begin + (it_begin + it) * BK, bar, stream_policy);
             }
-            pdl_wait();
-            for (int it = 0; it < prologue; ++it) {
-                const uint32_t bar = smem_u32(&full_bar[it]);
-                mbar_expect_tx(bar, A_STAGE_BYTES);
-                tma_load_2d(a_base + it * A_STAGE_BYTES, &map_a, p.k_begin + (it_begin + it) * BK, m0, bar);
+        }
+        __syncwarp();
+        pdl_wait();
+        for (int it = 0; it < prologue; ++it) copy_activations(it, p.k_begin + (it_begin + it) * BK);
+        for (int it = STAGES; it < n_iters; ++it) {
+            const int s = it % STAGES;
+            if (!mbar_wait(smem_u32(&empty_bar[s]), ((it / STAGES) - 1) & 1)) {
+                if (lane == 0) report_timeout(p.status, kKernelDecode, 1);
+                break;
             }
-            for (int it = STAGES; it < n_iters; ++it) {
-                const int s = it % STAGES;
-                if (!mbar_wait(smem_u32(&empty_bar[s]), ((it / STAGES) - 1) & 1)) {
-                    report_timeout(p.status, kKernelDecode, 1);
-                    break;
-                }
+            const int k0 = p.k_begin + (it_begin + it) * BK;
+            if (lane == 0) {
                 const uint32_t bar = smem_u32(&full_bar[s]);
-                const int k0 = p.k_begin + (it_begin + it) * BK;
                 mbar_expect_tx(bar, W_STAGE_BYTES);
                 tma_load_2d_hint(w_base + s * W_STAGE_BYTES, &map_w, NK ? k0 : n0, NK ? n0 : k0, bar, stream_policy);
-                mbar_expect_tx(bar, A_STAGE_BYTES);
-                tma_load_2d(a_base + s * A_STAGE_BYTES, &map_a, k0, m0, bar);
             }
-        } else {
-            pdl_wait();
+            copy_activations(s, k0);
         }
     } else {
         // ---------------- consumers ----------------
@@ -574,17 +603,16 @@ int launch_decode_kn(const void *a, const void *wq, const void *scale, void *c, 
     }
     if (pl.m_tiles > 65535 || pl.splits > 65535) return set_error(B200Q_UNSUPPORTED, "qlinear: M=%lld is too large for the small-M kernel", (long long)M);
 
-    CUtensorMap map_w, map_a;
+    CUtensorMap map_w;
     int rc = weight_nk ? make_tensor_map_2d(&map_w, CU_TENSOR_MAP_DATA_TYPE_UINT8, wq, (uint64_t)k_end, (uint64_t)N, (uint64_t)K, BK, BN,
                                             CU_TENSOR_MAP_SWIZZLE_64B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B)
                        : make_tensor_map_2d(&map_w, CU_TENSOR_MAP_DATA_TYPE_UINT8, wq, (uint64_t)N, (uint64_t)k_end, (uint64_t)N, BN, BK,
                                             CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B);
     if (rc != B200Q_OK) return rc;
-    rc = make_tensor_map_2d(&map_a, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, a, (uint64_t)k_end, (uint64_t)M, (uint64_t)K * 2, BK, BM,
-                            CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B);
-    if (rc != B200Q_OK) return rc;
 
     Params p;
+    p.a = static_cast<const __half *>(a);
+    p.lda = K;
     p.scale = static_cast<const __half *>(scale);
     if (targets != nullptr) {
         p.out = *targets;
@@ -636,7 +664,7 @@ int launch_decode_kn(const void *a, const void *wq, const void *scale, void *c, 
     attrs[1].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attrs;
     cfg.numAttrs = 2;
-    B200Q_CUDA_TRY(cudaLaunchKernelEx(&cfg, kernel, map_w, map_a, p));
+    B200Q_CUDA_TRY(cudaLaunchKernelEx(&cfg, kernel, map_w, p));
     return B200Q_OK;
 }
 

@@ -130,6 +130,14 @@ SIGNATURES = {
         c_int,
         True,
     ),
+    'b200q_qlinear_f16_u4_workspace_bytes': ([c_int64, c_int64, c_int64, c_int64], c_size_t, False),
+    'b200q_qlinear_f16_u4': (
+        [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64, c_int64, c_void_p, c_size_t, c_void_p],
+        c_int,
+        True,
+    ),
+    'b200q_u4_pack': ([c_void_p, c_void_p, c_int64, c_int64, c_void_p], c_int, True),
+    'b200q_u4_unpack': ([c_void_p, c_void_p, c_int64, c_int64, c_void_p], c_int, True),
     'b200q_qlinear_workspace_bytes': ([c_int64, c_int64, c_int64, c_int], c_size_t, False),
     'b200q_qlinear_f16_i8': (
         [c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64, c_int, c_void_p, c_size_t, c_void_p],

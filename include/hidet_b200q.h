@@ -23,8 +23,10 @@
  *     (every other kernel of this library, memcpy / memset nodes, anything that does not itself execute
  *     griddepcontrol.launch_dependents) let dependents start only when they have finished, so producing a
  *     weight with b200q_symmetric_quantize and using it in the next call on the same stream is safe.  Not
- *     safe: writing `wq` or `scale` from a kernel that triggers its dependents early, directly in front of
- *     a quantized linear on the same stream; put an event or any ordinary kernel between the two.
+ *     safe: writing `wq` or `scale` from a kernel that triggers its dependents early when nothing but
+ *     kernels of that kind lie between it and the quantized linear that reads them on the same stream (the
+ *     quantized-linear kernels are themselves of that kind: they let the next kernel start while they
+ *     run); put an event or any ordinary kernel between the two.
  *   - matrices are dense row-major.  "KN" weight layout = [K, N] with N contiguous, the layout of
  *     the reference operator (python/hidet/graph/ops/quant/matmul.py:30-32); "NK" = [N, K] with K
  *     contiguous, the layout torch.nn.Linear stores.
@@ -110,6 +112,31 @@ B200Q_API int b200q_symmetric_dequantize(const void *wq, const void *scale, void
 B200Q_API int b200q_embedding_dequantize(const void *table, const void *scale, const void *indices, void *out, int64_t vocab,
                                          int64_t dim, int64_t n_indices, int scale_type /* b200q_float_type */,
                                          int q_type /* b200q_quant_type */, int index_bytes, void *stream);
+
+/*
+ * Sub-byte weights (w4a16): 4-bit unsigned codes with per-group scales and optional zero points, the format of the
+ * reference's CuTe test programs (tests/cute_kernel/quantized_linear.py:494-517, its check at
+ * tests/cute_kernel/test_quant_linear.py:68-85):
+ *     c[M, N] = a[M, K] x w[K, N],   w[k, n] = scale[k / G, n] * (q[k, n] - zeros[k / G, n])
+ * a f16 [M, K]; q u4 [K, N] packed two codes per byte, element i of a row in bits 4 (i % 2) .. + 3 of byte i / 2
+ * (the reference's sub-byte storage, python/hidet/transforms/lower_integer_subbyte.py:103-113), row-major, as
+ * b200q_u4_pack / the reference's cast_f16_to_u4 produce it (not the kernel-private layout of its
+ * preprocess_weight); scale, zeros f16 [K / G, N] (zeros may be NULL: w = scale * q); c f16 [M, N].
+ * K must be a multiple of the group size G, N a multiple of 8.  Sums are fp32, the order of every sum is fixed.
+ * The workspace (b200q_qlinear_f16_u4_workspace_bytes) holds fp32 partial sums behind an untouched head of 256 KB
+ * (where b200q_qlinear_f16_i8 keeps its counters, so that one workspace can serve both) and needs no initialisation.
+ */
+B200Q_API size_t b200q_qlinear_f16_u4_workspace_bytes(int64_t M, int64_t N, int64_t K, int64_t group_size);
+B200Q_API int b200q_qlinear_f16_u4(const void *a, const void *q, const void *scale, const void *zeros, void *c, int64_t M, int64_t N,
+                                   int64_t K, int64_t group_size, void *workspace, size_t workspace_bytes, void *stream);
+
+/*
+ * u4 codes <-> f16: b200q_u4_pack converts f16 [rows, cols] to int the way C does and keeps the low four bits
+ * (the reference's cast_f16_to_u4, tests/cute_kernel/quantized_linear.py:226-267), two codes per byte as above;
+ * b200q_u4_unpack is the inverse (cast_u4_to_f16, :181-223).  cols must be even.
+ */
+B200Q_API int b200q_u4_pack(const void *w, void *packed, int64_t rows, int64_t cols, void *stream);
+B200Q_API int b200q_u4_unpack(const void *packed, void *w, int64_t rows, int64_t cols, void *stream);
 
 /*
  * Bytes of scratch b200q_qlinear_f16_i8 needs for this problem (0 is a valid answer).

@@ -56,6 +56,9 @@ def test_llama_7b_shaped_decoder_at_full_size():
     cfg = bench_decoder.DecoderConfig(steps=16)   # the full model; fewer steps than the benchmark's 128
     out = bench_decoder.run_config(cfg, parity_steps=8)
     # the oracle is the fp32 decoder on dequantized weights; the eager fp16 decoder's own distance from it is reported beside
-    assert out['parity']['max_abs_err_over_max_ref'] <= 1e-2, out['parity']
-    assert out['parity']['argmax_agreement'] >= 0.75, out['parity']   # 9 passes over random weights: near-ties are common
+    # 1e-2 of the largest logit, or (the model being 32 fp16 layers deep) what the eager fp16 decoder on the same
+    # weights is off by, with a quarter on top: the int8 path is to add nothing beyond fp16's own rounding
+    parity = out['parity']
+    assert parity['max_abs_err_over_max_ref'] <= max(1e-2, 1.25 * parity['eager_f16_max_abs_err_over_max_ref']), parity
+    assert parity['argmax_agreement'] >= 0.75, parity   # 9 passes over random weights: near-ties are common
     assert out['generated_tokens'] == 16 and out['prompt_ms'] > 0 and out['ms_per_decode_step'] > 0
