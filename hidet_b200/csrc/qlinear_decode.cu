@@ -563,6 +563,10 @@ DecodePlan plan_decode(int64_t M, int64_t N, int64_t K) {
     int c = (int)(splits < kMaxCluster ? splits : kMaxCluster);
     int groups = (int)(splits / c);
     if (groups < 1 || tiles * c > kMaxCounters) groups = 1;
+    // Clusters that meet in the workspace pay three dependent trips through L2 at the end of the launch (publish,
+    // count, read back), about 3 us more than partials that meet in distributed shared memory.  That is worth it only
+    // when one cluster per tile would leave most of the machine idle.
+    if (groups > 1 && tiles * c * 2 >= sms) groups = 1;
     pl.cluster = c;
     pl.groups = groups;
     pl.splits = c * groups;  // the grid holds whole clusters; a split may get fewer steps than others, or none

@@ -568,7 +568,17 @@ int launch_prefill_kn(const void *a, const void *wq, const void *scale, void *c,
                       cudaStream_t stream, const OutTargets *targets, const Epilogue *epilogue, bool weight_nk) {
     int sms = sm_count();
     if (sms <= 0) sms = 148;
-    switch (choose_tile_m(M, N, sms)) {
+    int tm = choose_tile_m(M, N, sms);
+    if (tm == 256 && targets != nullptr && targets->count > 1) {
+        // Peer delivery: a tile's rows leave for the other GPUs only when the tile is finished, so with tall tiles the
+        // links idle during the first tile and carry everything in what is left.  When the bytes that have to leave
+        // (at about 700 GB/s) weigh as much as the product itself, short tiles start the delivery early and spread
+        // it over the whole launch; that is worth more than the tall tiles' better tensor-core rate.
+        const double compute_us = 2.0 * (double)M * (double)N * (double)K / 900e6;
+        const double delivery_us = (double)M * (double)N * 2.0 * (double)(targets->count - 1) / 700e3;
+        if (delivery_us > 0.6 * compute_us) tm = 64;
+    }
+    switch (tm) {
         case 64: return launch_prefill_tm<64>(a, wq, scale, c, M, N, K, stream, targets, epilogue, sms, weight_nk);
         default: return launch_prefill_tm<256>(a, wq, scale, c, M, N, K, stream, targets, epilogue, sms, weight_nk);
     }
