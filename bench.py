@@ -601,6 +601,8 @@ def main(argv=None) -> int:
     ap.add_argument('--no-extras', action='store_true', help='skip the prefill and quantize sections (for profiling runs)')
     ap.add_argument('--gather', choices=['nccl', 'p2p'], default=None,
                     help='multi-GPU: how output slices reach every rank (default: p2p up to four GPUs, nccl on eight)')
+    ap.add_argument('--multicast', choices=['on', 'off'], default='on',
+                    help='multi-GPU, --gather p2p: deliver large M through the NVLink multicast mapping of the outputs where there is one')
     ap.add_argument('--m-list', default=None, help='multi-GPU: comma-separated activation row counts to sweep instead of 1,16,256,2048')
     ap.add_argument('--record-traffic', nargs='+', default=None, metavar='CSV',
                     help='no benchmark: read ncu CSV logs (decode_M,K,N.csv) and write profiles/qlinear_decode_dram_traffic.json')

@@ -223,8 +223,40 @@ def run_config(cfg: DecoderConfig = LLAMA_7B, parity_steps: int = 8, seed: int =
         weight_bytes = sum(m.weight.numel() for m in model.modules() if isinstance(m, nn.Linear))
         out['int8_weight_bytes_per_step'] = weight_bytes
         out['weight_stream_GBps'] = round(weight_bytes / (decode_ms / cfg.steps * 1e-3) / 1e9, 1)
+        out['kernel_time_of_a_step'] = kernel_time_of_a_step(step_graph)
         assert hidet_b200.ffi.func('b200q_check_status')() == hidet_b200.ffi.OK
     return out
+
+
+def kernel_time_of_a_step(step_graph, replays: int = 3):
+    """Device time of the kernels of one decode step by kind, from torch.profiler's kernel records of a few replays of
+    the step's CUDA graph: how much of the step is the quantized-linear path and how much the rest of the decoder
+    (attention, normalisation, rotary embedding and the other element-wise kernels torch launches).  None when the
+    profiler gives no kernel records."""
+    try:
+        from torch.profiler import ProfilerActivity, profile
+
+        with profile(activities=[ProfilerActivity.CUDA]) as prof:
+            for _ in range(replays):
+                step_graph.run_async()
+            torch.cuda.synchronize()
+        kinds = {'qlinear': 0.0, 'embedding_dequant': 0.0, 'other': 0.0}
+        launches = {'qlinear': 0, 'embedding_dequant': 0, 'other': 0}
+        for row in prof.key_averages():
+            t = float(getattr(row, 'device_time_total', 0.0) or getattr(row, 'cuda_time_total', 0.0) or 0.0)
+            if t <= 0.0:
+                continue
+            kind = 'qlinear' if 'qlinear' in row.key else 'embedding_dequant' if 'embedding_dequant' in row.key else 'other'
+            kinds[kind] += t
+            launches[kind] += int(row.count)
+        total = sum(kinds.values())
+        if total <= 0.0:
+            return None
+        return {'us_per_step': {k: round(v / replays, 1) for k, v in kinds.items()},
+                'launches_per_step': {k: v // replays for k, v in launches.items()},
+                'share_of_kernel_time_in_the_quantized_path': round((kinds['qlinear'] + kinds['embedding_dequant']) / total, 4)}
+    except Exception as e:  # the profiler is optional equipment
+        return {'unavailable': '{}: {}'.format(type(e).__name__, e)}
 
 
 if __name__ == '__main__':

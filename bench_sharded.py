@@ -28,9 +28,13 @@ def run_sharded(args) -> int:
     import hidet_b200
     from hidet_b200.distributed import ColumnParallelQuantLinear, column_range
 
-    # Plain peer mappings only: the outputs are written with ordinary stores, and memory bound to an NVLink
-    # multicast object must not be left behind by a rank that ends early.
-    os.environ.setdefault('TORCH_SYMM_MEM_DISABLE_MULTICAST', '1')
+    multicast = getattr(args, 'multicast', 'on') == 'on'
+    if not multicast:
+        # Plain peer mappings only: the outputs are written with ordinary stores.
+        os.environ.setdefault('TORCH_SYMM_MEM_DISABLE_MULTICAST', '1')
+    # (With multicast on, the outputs are also bound to an NVLink multicast object where the system has one, and large
+    # M is delivered by single stores to it.  Memory bound to such an object must not be left behind by a rank that
+    # ends early: every rank releases its layers before the process group goes, see the end of this function.)
     rank = int(os.environ.get('RANK', '0'))
     world = int(os.environ.get('WORLD_SIZE', str(args.gpus)))
     local_rank = int(os.environ.get('LOCAL_RANK', str(rank)))
@@ -58,7 +62,7 @@ def run_sharded(args) -> int:
     for i in range(copies):
         gen = torch.Generator(device=device).manual_seed(100 + i)
         w = (torch.randn(k, n, generator=gen, device=device, dtype=torch.float32) * 0.02).to(torch.float16)
-        layers.append(ColumnParallelQuantLinear.from_weight_shard(w[:, begin:end].contiguous(), gather=args.gather))
+        layers.append(ColumnParallelQuantLinear.from_weight_shard(w[:, begin:end].contiguous(), gather=args.gather, multicast=multicast))
         if args.gather == 'p2p' and i > 0:
             layers[-1].share_outputs_with(layers[0])
         del w
@@ -231,11 +235,15 @@ def run_sharded(args) -> int:
     assert hidet_b200.ffi.func('b200q_check_status')() == 0
 
     if rank == 0:
+        uses_multicast = args.gather == 'p2p' and any(po.multicast_ptrs and po.multicast_ptrs[0] for layer in layers for po in layer._peer_outputs.values())
+        large_m_delivery = ('one multimem.st per 16 bytes to the NVLink multicast mapping of the outputs' if uses_multicast and multicast
+                            else 'peer stores to every rank' if args.gather == 'p2p' else 'NCCL all-gather')
         line = {
             'metric': 'quant-linear HBM GB/s (70B-shaped layer, column-parallel)', 'value': value, 'unit': 'GB/s', 'n_gpus': world,
             'steps': args.steps, 'warmup': max(args.warmup, 3), 'ms_per_step': ms_per_step, 'higher_is_better': True,
             'scaling': 'strong', 'vs_baseline': None, 'dtype': 'f16', 'accumulate': 'f32', 'weight_dtype': 'i8', 'data': 'synthetic',
             'config': {'workload': 'sharded-70b-layer', 'K': k, 'N': n, 'M': list(MS_70B), 'parallelism': 'tp{} (columns), outputs by {}'.format(world, 'peer stores from the kernels\' epilogues + one cross-rank barrier' if args.gather == 'p2p' else 'NCCL all-gather'),
+                       'large_m_delivery': large_m_delivery,
                        'weights_in_rotation': copies, 'l2': 'inputs larger than L2: {} distinct weight shards of {} MB per rank'.format(copies, k * n_local // 1000000),
                        'timing': timing + ', CUDA events, barrier on both sides, max over ranks'},
             'tflops': flops_per_step / (ms_per_step * 1e-3) / 1e12,

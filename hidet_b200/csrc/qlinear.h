@@ -13,10 +13,13 @@ namespace b200q {
 // column-parallel layer delivers its slice to every rank without a separate all-gather.
 constexpr int kMaxOutTargets = 8;
 struct OutTargets {
-    void *ptr[kMaxOutTargets];
-    int count;
-    int64_t ldc;   // elements between consecutive rows of the destination
-    int64_t col0;  // first destination column
+    void *ptr[kMaxOutTargets] = {};
+    int count = 0;
+    int64_t ldc = 0;   // elements between consecutive rows of the destination
+    int64_t col0 = 0;  // first destination column
+    // ptr[0] is an NVLink multicast address (one store reaches the same place of every GPU bound to it, this one
+    // included); count is 1.  Served by the large-M kernel only, whose epilogue then stores with multimem.st.
+    int multicast = 0;
 };
 
 // What a kernel does to the scaled fp32 sums y[m, n] before the one rounding to f16:
@@ -59,8 +62,20 @@ bool decode_nk_supported(const void *a, const void *wq, int64_t N, int64_t K);
 
 // The tensor-memory kernel for large M: same operand requirements as the small-M kernel.
 bool prefill_kn_supported(const void *a, const void *wq, int64_t N, int64_t K);
+// How the tensor-memory kernel splits K (narrow problems only) and the scratch that takes: fp32 partial sums
+// [k_splits][M][N] behind an untouched head of kSplitWorkspaceHead bytes (the small-M kernel's counters live there).
+constexpr size_t kSplitWorkspaceHead = (size_t)65536 * 4;
+struct PrefillSplit {
+    int k_splits = 1;
+    int kb_per_split = 0;
+    size_t workspace_bytes = 0;
+};
+PrefillSplit plan_prefill_split(int64_t M, int64_t N, int64_t K);
+// lda: elements between rows of `a` when they are longer than K (a k range of wider activations); 0 = K.
+// workspace: where K may be split (see plan_prefill_split); without it the kernel runs one CTA per output tile.
 int launch_prefill_kn(const void *a, const void *wq, const void *scale, void *c, int64_t M, int64_t N, int64_t K,
-                      cudaStream_t stream, const OutTargets *targets = nullptr, const Epilogue *epilogue = nullptr, bool weight_nk = false);
+                      cudaStream_t stream, const OutTargets *targets = nullptr, const Epilogue *epilogue = nullptr, bool weight_nk = false,
+                      int64_t lda = 0, void *workspace = nullptr, size_t workspace_bytes = 0);
 // The same kernel on a weight stored [N, K] (weight_nk = true): 16-byte aligned bases, K % 16 == 0, N % 8 == 0.
 bool prefill_nk_supported(const void *a, const void *wq, int64_t N, int64_t K);
 

@@ -62,7 +62,14 @@ B200Q_API size_t b200q_qlinear_workspace_bytes(int64_t M, int64_t N, int64_t K, 
     (void)w_layout;
     if (M <= 0 || N <= 0 || K <= 0) return 0;
     const DecodePlan pl = plan_decode(M, N, K);
-    return pl.counter_bytes + pl.partial_bytes;
+    size_t need = pl.counter_bytes + pl.partial_bytes;
+    if (use_prefill_kernel(M, N, K)) {
+        // the tensor-memory kernel needs scratch only when it splits K; operands it cannot take (alignment is not
+        // known here) go to the small-M kernel, so its need is covered as well
+        const size_t split = plan_prefill_split(M, N, K).workspace_bytes;
+        if (split > need) need = split;
+    }
+    return need;
 }
 
 B200Q_API int b200q_qlinear_f16_i8(const void *a, const void *wq, const void *scale, void *c, int64_t M, int64_t N,
@@ -77,10 +84,10 @@ B200Q_API int b200q_qlinear_f16_i8(const void *a, const void *wq, const void *sc
         return B200Q_OK;
     }
     if (w_layout == B200Q_LAYOUT_KN && use_prefill_kernel(M, N, K) && prefill_kn_supported(a, wq, N, K)) {
-        return launch_prefill_kn(a, wq, scale, c, M, N, K, s);
+        return launch_prefill_kn(a, wq, scale, c, M, N, K, s, nullptr, nullptr, false, 0, workspace, workspace_bytes);
     }
     if (w_layout == B200Q_LAYOUT_NK && use_prefill_kernel(M, N, K) && prefill_nk_supported(a, wq, N, K)) {
-        return launch_prefill_kn(a, wq, scale, c, M, N, K, s, nullptr, nullptr, true);
+        return launch_prefill_kn(a, wq, scale, c, M, N, K, s, nullptr, nullptr, true, 0, workspace, workspace_bytes);
     }
     if (w_layout == B200Q_LAYOUT_KN && decode_kn_supported(a, wq, N, K)) {
         return launch_decode_kn(a, wq, scale, c, M, N, K, 0, K, true, workspace, workspace_bytes, s);
@@ -117,7 +124,7 @@ B200Q_API int b200q_qlinear_f16_i8_fused(const void *a, const void *wq, const vo
     ep.ldr = epilogue->ldr;
     ep.act = pairs ? kActSiluMul : kActNone;
     cudaStream_t s = static_cast<cudaStream_t>(stream);
-    if (use_prefill_kernel(M, N, K)) return launch_prefill_kn(a, wq, scale, c, M, N, K, s, nullptr, &ep);
+    if (use_prefill_kernel(M, N, K)) return launch_prefill_kn(a, wq, scale, c, M, N, K, s, nullptr, &ep, false, 0, workspace, workspace_bytes);
     return launch_decode_kn(a, wq, scale, c, M, N, K, 0, K, true, workspace, workspace_bytes, s, nullptr, &ep);
 }
 
@@ -144,8 +151,32 @@ B200Q_API int b200q_qlinear_f16_i8_to_peers(const void *a, const void *wq, const
     if (!decode_kn_supported(a, wq, N, K)) {
         return set_error(B200Q_UNSUPPORTED, "qlinear_f16_i8_to_peers: operands need 16-byte aligned bases and rows (N %% 16 == 0, K %% 8 == 0)");
     }
-    if (use_prefill_kernel(M, N, K)) return launch_prefill_kn(a, wq, scale, dst[0], M, N, K, s, &t);
+    if (use_prefill_kernel(M, N, K)) return launch_prefill_kn(a, wq, scale, dst[0], M, N, K, s, &t, nullptr, false, 0, workspace, workspace_bytes);
     return launch_decode_kn(a, wq, scale, dst[0], M, N, K, 0, K, true, workspace, workspace_bytes, s, &t);
+}
+
+B200Q_API int b200q_qlinear_f16_i8_to_multicast(const void *a, const void *wq, const void *scale, void *multicast_dst, int64_t ldc,
+                                                int64_t col_offset, int64_t M, int64_t N, int64_t K, void *workspace, size_t workspace_bytes,
+                                                void *stream) {
+    using namespace b200q;
+    if (multicast_dst == nullptr) return set_error(B200Q_INVALID_ARGUMENT, "qlinear_f16_i8_to_multicast: null destination");
+    if (col_offset < 0 || ldc < col_offset + N) return set_error(B200Q_INVALID_ARGUMENT, "qlinear_f16_i8_to_multicast: columns [%lld, %lld) do not fit rows of %lld elements", (long long)col_offset, (long long)(col_offset + N), (long long)ldc);
+    int rc = check_qlinear_args("qlinear_f16_i8_to_multicast", a, wq, scale, multicast_dst, M, N, K, B200Q_LAYOUT_KN);
+    if (rc != B200Q_OK) return rc;
+    if (M == 0 || N == 0) return B200Q_OK;
+    if (K == 0) return set_error(B200Q_INVALID_ARGUMENT, "qlinear_f16_i8_to_multicast: K must be positive");
+    if (!use_prefill_kernel(M, N, K) || !prefill_kn_supported(a, wq, N, K)) {
+        return set_error(B200Q_UNSUPPORTED, "qlinear_f16_i8_to_multicast: served by the large-M kernel only (M >= %lld, 16-byte aligned operands, "
+                                            "N %% 16 == 0, K %% 8 == 0); use b200q_qlinear_f16_i8_to_peers for M=%lld N=%lld K=%lld",
+                         (long long)kPrefillMinM, (long long)M, (long long)N, (long long)K);
+    }
+    OutTargets t;
+    t.ptr[0] = multicast_dst;
+    t.count = 1;
+    t.ldc = ldc;
+    t.col0 = col_offset;
+    t.multicast = 1;
+    return launch_prefill_kn(a, wq, scale, multicast_dst, M, N, K, static_cast<cudaStream_t>(stream), &t, nullptr, false, 0, workspace, workspace_bytes);
 }
 
 B200Q_API int b200q_qlinear_f16_i8_parts(const void *a, const void *wq, const void *scale, void *c, int64_t M,
@@ -169,8 +200,16 @@ B200Q_API int b200q_qlinear_f16_i8_parts(const void *a, const void *wq, const vo
             B200Q_CUDA_TRY(cudaMemsetAsync(cp, 0, (size_t)M * N * sizeof(__half), s));
             continue;
         }
-        rc = fast ? launch_decode_kn(a, wq, scale, cp, M, N, K, k_begin, k_end, false, nullptr, 0, s)
-                  : launch_generic(a, wq, scale, cp, M, N, K, k_begin, k_end, B200Q_LAYOUT_KN, s);
+        // Large M: the tensor-memory kernel on the k range as a problem of its own (activation columns k_begin ..
+        // of rows that stay K long, weight rows k_begin ..); small M: the streaming kernel on the range.
+        const __half *a_part = static_cast<const __half *>(a) + k_begin;
+        const int8_t *w_part = static_cast<const int8_t *>(wq) + (size_t)k_begin * N;
+        if (fast && use_prefill_kernel(M, N, k_end - k_begin) && prefill_kn_supported(a_part, w_part, N, k_end - k_begin)) {
+            rc = launch_prefill_kn(a_part, w_part, scale, cp, M, N, k_end - k_begin, s, nullptr, nullptr, false, K);
+        } else {
+            rc = fast ? launch_decode_kn(a, wq, scale, cp, M, N, K, k_begin, k_end, false, nullptr, 0, s)
+                      : launch_generic(a, wq, scale, cp, M, N, K, k_begin, k_end, B200Q_LAYOUT_KN, s);
+        }
         if (rc != B200Q_OK) return rc;
     }
     return B200Q_OK;

@@ -146,6 +146,11 @@ struct Params {
     unsigned int *status;
     int M, N, K;
     int n_tiles, m_tiles;
+    // K split over several CTAs per output tile (narrow problems that would leave most SMs idle): a tile index is
+    // (output tile, split); split s sums k blocks [s * kb_per_split, ...) and writes raw fp32 sums to
+    // partial[s][M][N]; qlinear_prefill_reduce_kernel adds the splits and finishes.  k_splits == 1: no partial.
+    int k_splits, kb_per_split;
+    float *partial;
 };
 
 // FUSED: the epilogue of p.ep (bias, gate / up pairing, residual) is compiled in.
@@ -191,8 +196,11 @@ __global__ void __launch_bounds__(THREADS, 1) qlinear_prefill_kn_kernel(const __
     unsigned char *smem_gen = smem_dyn + (smem_base - smem_u32(smem_dyn));
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
-    const int total_tiles = p.n_tiles * p.m_tiles;
+    const int total_tiles = p.n_tiles * p.m_tiles * p.k_splits;
     const int k_blocks = (p.K + BK - 1) / BK;
+    // tile index -> output tile and k-block range
+    auto kb_first = [&](int tile) { return (tile % p.k_splits) * p.kb_per_split; };
+    auto kb_last = [&](int tile) { return min(k_blocks, (tile % p.k_splits + 1) * p.kb_per_split); };
 
     // layout: STAGES x [activations][f16 weights], RAW_SLOTS x [int8 weights], epilogue staging
     auto act_addr = [&](int s) { return smem_base + s * Cfg::MAIN_BYTES; };
@@ -245,9 +253,10 @@ __global__ void __launch_bounds__(THREADS, 1) qlinear_prefill_kn_kernel(const __
             bool ok = true;
             uint32_t n_raw = 0, n_act = 0;  // copies armed so far (stages 0 .. n - 1), for the teardown
             for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
-                const int n0 = (tile % p.n_tiles) * TN;
-                const int m0 = (tile / p.n_tiles) * TM;
-                for (int kb = 0; kb < k_blocks; ++kb, ++i) {
+                const int otile = tile / p.k_splits;
+                const int n0 = (otile % p.n_tiles) * TN;
+                const int m0 = (otile / p.n_tiles) * TM;
+                for (int kb = kb_first(tile), kb_end = kb_last(tile); kb < kb_end; ++kb, ++i) {
                     const int r = i % RAW_SLOTS;
                     const uint32_t use_r = i / RAW_SLOTS;
                     if (use_r >= 1 && !wait(smem_u32(&raw_empty[r]), (use_r - 1) & 1, 1)) {
@@ -293,7 +302,8 @@ __global__ void __launch_bounds__(THREADS, 1) qlinear_prefill_kn_kernel(const __
                 if (acc_use >= 1 && !wait(smem_u32(&acc_empty[buf]), (acc_use - 1) & 1, 2)) break;
                 tc_fence_after_sync();
                 const uint32_t d_addr = tmem_base + buf * TM;
-                for (int kb = 0; kb < k_blocks; ++kb, ++i) {
+                const int kb_begin = kb_first(tile);
+                for (int kb = kb_begin, kb_end = kb_last(tile); kb < kb_end; ++kb, ++i) {
                     const int s = i % STAGES;
                     const uint32_t use = i / STAGES;
                     if (!wait(smem_u32(&act_full[s]), use & 1, 3) || !wait(smem_u32(&conv_full[s]), use & 1, 3)) {
@@ -308,7 +318,7 @@ __global__ void __launch_bounds__(THREADS, 1) qlinear_prefill_kn_kernel(const __
                         const uint64_t da = NK ? smem_desc(wf_addr(s) + ks * 32, 16, 1024) : smem_desc(wf_addr(s) + ks * 2048, 8192, 1024);
                         // B: K-major activations, 8-row groups 1024 B apart; K = 16 is 32 bytes along the swizzled row.
                         const uint64_t db = smem_desc(act_addr(s) + ks * 32, 16, 1024);
-                        umma_f16(d_addr, da, db, NK ? Cfg::kInstrDescNK : Cfg::kInstrDesc, (kb > 0 || ks > 0) ? 1u : 0u);
+                        umma_f16(d_addr, da, db, NK ? Cfg::kInstrDescNK : Cfg::kInstrDesc, (kb > kb_begin || ks > 0) ? 1u : 0u);
                     }
                     umma_commit(smem_u32(&slot_free[s]));
                 }
@@ -333,7 +343,7 @@ __global__ void __launch_bounds__(THREADS, 1) qlinear_prefill_kn_kernel(const __
         uint32_t i = 0;
         bool ok = true;
         for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
-            for (int kb = 0; kb < k_blocks; ++kb, ++i) {
+            for (int kb = kb_first(tile), kb_end = kb_last(tile); kb < kb_end; ++kb, ++i) {
                 if ((int)(i % CONV_GROUPS) != group) continue;
                 const int r = i % RAW_SLOTS;
                 const uint32_t use_r = i / RAW_SLOTS;
@@ -405,12 +415,35 @@ __global__ void __launch_bounds__(THREADS, 1) qlinear_prefill_kn_kernel(const __
         const int row_in_pass = et >> 4;
         uint32_t t_iter = 0;
         for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x, ++t_iter) {
-            const int n0 = (tile % p.n_tiles) * TN;
-            const int m0 = (tile / p.n_tiles) * TM;
+            const int otile = tile / p.k_splits;
+            const int n0 = (otile % p.n_tiles) * TN;
+            const int m0 = (otile / p.n_tiles) * TM;
             const uint32_t buf = t_iter & 1, acc_use = t_iter >> 1;
             if (!wait(smem_u32(&acc_full[buf]), acc_use & 1, 5)) break;
             tc_fence_after_sync();
             const int n = n0 + 32 * q + lane;
+            if (p.k_splits > 1) {
+                // Split K: the raw fp32 sums of this split go to the workspace (lane = column, so every store of a warp is
+                // 128 contiguous bytes); scales, epilogue and rounding happen once, in the reduce kernel.
+                float *dst = p.partial + ((size_t)(tile % p.k_splits) * p.M + m0) * p.N + n;
+                const int m_left = p.M - m0;
+#pragma unroll 1
+                for (int cb = 0; cb < TM / 32; ++cb) {
+                    if (cb * 32 >= m_left) break;
+                    uint32_t v[32];
+                    tmem_ld_32x32(tmem_base + ((uint32_t)(32 * q) << 16) + buf * TM + cb * 32, v);
+                    tmem_ld_wait();
+                    if (n < p.N) {
+#pragma unroll
+                        for (int j = 0; j < 32; ++j)
+                            if (cb * 32 + j < m_left) __stcg(dst + (size_t)(cb * 32 + j) * p.N, __uint_as_float(v[j]));
+                    }
+                }
+                tc_fence_before_sync();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(smem_u32(&acc_empty[buf]));
+                continue;
+            }
             const float sc = n < p.N ? __half2float(p.scale[n]) : 0.0f;
             const float bias = (FUSED && n < p.N && p.ep.bias != nullptr) ? __half2float(__ldg(static_cast<const __half *>(p.ep.bias) + n)) : 0.0f;
             const bool pairs = FUSED && p.ep.act == kActSiluMul;  // columns (2j, 2j + 1) = (gate, up): the even lane finishes both
@@ -450,8 +483,15 @@ __global__ void __launch_bounds__(THREADS, 1) qlinear_prefill_kn_kernel(const __
                         const size_t off = (size_t)(m0 + m) * p.out.ldc + col_off;
                         // every destination: this GPU's output and, for a column-parallel layer, the peer-mapped
                         // outputs of the other ranks (plain 16-byte stores over NVLink, no loads)
+                        if (p.out.multicast) {
+                            // one store to the multicast address: the switch delivers it to every GPU of the group
+                            asm volatile("multimem.st.weak.global.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(static_cast<__half *>(p.out.ptr[0]) + off),
+                                         "f"(__uint_as_float(val.x)), "f"(__uint_as_float(val.y)), "f"(__uint_as_float(val.z)), "f"(__uint_as_float(val.w))
+                                         : "memory");
+                        } else {
 #pragma unroll 1
-                        for (int d = 0; d < p.out.count; ++d) *reinterpret_cast<uint4 *>(static_cast<__half *>(p.out.ptr[d]) + off) = val;
+                            for (int d = 0; d < p.out.count; ++d) *reinterpret_cast<uint4 *>(static_cast<__half *>(p.out.ptr[d]) + off) = val;
+                        }
                     }
                 }
                 asm volatile("bar.sync 1, 128;" ::: "memory");  // staging may be overwritten
@@ -468,6 +508,72 @@ __global__ void __launch_bounds__(THREADS, 1) qlinear_prefill_kn_kernel(const __
     if (warp == MMA_WARP) {
         tc_fence_after_sync();
         tmem_dealloc(tmem_base, Cfg::TMEM_COLS);
+    }
+}
+
+// Adds the k_splits partial sums of every output element in split order, then does what the epilogue does: scale,
+// bias, gate / up pairing, residual, one rounding, 16-byte stores to every destination.  A thread owns eight adjacent
+// columns of one row.
+__global__ void __launch_bounds__(256) qlinear_prefill_reduce_kernel(const float *__restrict__ partial, const __half *__restrict__ scale,
+                                                                     OutTargets out, Epilogue ep, int M, int N, int k_splits) {
+    const int64_t groups_per_row = N / 8;
+    const int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= (int64_t)M * groups_per_row) return;
+    const int m = (int)(idx / groups_per_row);
+    const int n = (int)(idx - (int64_t)m * groups_per_row) * 8;
+    float y[8];
+#pragma unroll
+    for (int c = 0; c < 8; ++c) y[c] = 0.0f;
+    const float *src = partial + (size_t)m * N + n;
+    for (int sp = 0; sp < k_splits; ++sp) {
+        const float4 v0 = __ldcg(reinterpret_cast<const float4 *>(src + (size_t)sp * M * N));
+        const float4 v1 = __ldcg(reinterpret_cast<const float4 *>(src + (size_t)sp * M * N + 4));
+        y[0] += v0.x, y[1] += v0.y, y[2] += v0.z, y[3] += v0.w;
+        y[4] += v1.x, y[5] += v1.y, y[6] += v1.z, y[7] += v1.w;
+    }
+    const uint4 sraw = __ldg(reinterpret_cast<const uint4 *>(scale + n));
+    const __half *sh = reinterpret_cast<const __half *>(&sraw);
+#pragma unroll
+    for (int c = 0; c < 8; ++c) y[c] *= __half2float(sh[c]);
+    if (ep.bias != nullptr) {
+        const uint4 braw = __ldg(reinterpret_cast<const uint4 *>(static_cast<const __half *>(ep.bias) + n));
+        const __half *bh = reinterpret_cast<const __half *>(&braw);
+#pragma unroll
+        for (int c = 0; c < 8; ++c) y[c] += __half2float(bh[c]);
+    }
+    if (ep.act == kActSiluMul) {
+        // columns (2j, 2j + 1) = (gate, up): four results per thread, result column n / 2 + j
+        __half2 r2[2];
+        float z[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            z[j] = y[2 * j] / (1.0f + __expf(-y[2 * j])) * y[2 * j + 1];
+            if (ep.residual != nullptr) z[j] += __half2float(__ldg(static_cast<const __half *>(ep.residual) + (size_t)m * ep.ldr + (n >> 1) + j));
+        }
+        r2[0] = __floats2half2_rn(z[0], z[1]);
+        r2[1] = __floats2half2_rn(z[2], z[3]);
+        const uint2 val = *reinterpret_cast<const uint2 *>(r2);
+        const size_t off = (size_t)m * out.ldc + out.col0 + (n >> 1);
+        for (int d = 0; d < out.count; ++d) *reinterpret_cast<uint2 *>(static_cast<__half *>(out.ptr[d]) + off) = val;
+        return;
+    }
+    if (ep.residual != nullptr) {
+        const uint4 rraw = __ldg(reinterpret_cast<const uint4 *>(static_cast<const __half *>(ep.residual) + (size_t)m * ep.ldr + n));
+        const __half *rh = reinterpret_cast<const __half *>(&rraw);
+#pragma unroll
+        for (int c = 0; c < 8; ++c) y[c] += __half2float(rh[c]);
+    }
+    __half2 h2[4];
+#pragma unroll
+    for (int c = 0; c < 4; ++c) h2[c] = __floats2half2_rn(y[2 * c], y[2 * c + 1]);
+    const uint4 val = *reinterpret_cast<const uint4 *>(h2);
+    const size_t off = (size_t)m * out.ldc + out.col0 + n;
+    if (out.multicast) {
+        asm volatile("multimem.st.weak.global.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(static_cast<__half *>(out.ptr[0]) + off), "f"(__uint_as_float(val.x)),
+                     "f"(__uint_as_float(val.y)), "f"(__uint_as_float(val.z)), "f"(__uint_as_float(val.w))
+                     : "memory");
+    } else {
+        for (int d = 0; d < out.count; ++d) *reinterpret_cast<uint4 *>(static_cast<__half *>(out.ptr[d]) + off) = val;
     }
 }
 
@@ -498,9 +604,30 @@ static int choose_tile_m(int64_t M, int64_t N, int sms) {
     return best;
 }
 
+// Split K over several CTAs per output tile when 256-row tiles alone would occupy less than half of the SMs and
+// there are enough k blocks to share out (a narrow column shard at a few hundred rows).  Splits come with 256-row
+// tiles; every split gets at least eight k blocks.
+PrefillSplit plan_prefill_split(int64_t M, int64_t N, int64_t K) {
+    PrefillSplit ps;
+    int sms = sm_count();
+    if (sms <= 0) sms = 148;
+    const int64_t tiles = ceil_div(N, prefill::TN) * ceil_div(M, 256);
+    const int64_t k_blocks = ceil_div(K, prefill::BK);
+    if (tiles * 2 > sms || k_blocks < 16 || N % 8 != 0) return ps;
+    int64_t splits = sms / tiles;
+    if (splits > k_blocks / 8) splits = k_blocks / 8;
+    if (splits < 2) return ps;
+    ps.kb_per_split = (int)ceil_div(k_blocks, splits);
+    ps.k_splits = (int)ceil_div(k_blocks, ps.kb_per_split);
+    if (ps.k_splits < 2) return PrefillSplit();
+    ps.workspace_bytes = kSplitWorkspaceHead + (size_t)ps.k_splits * M * N * sizeof(float);
+    return ps;
+}
+
 template <int TM>
 static int launch_prefill_tm(const void *a, const void *wq, const void *scale, void *c, int64_t M, int64_t N, int64_t K,
-                             cudaStream_t stream, const OutTargets *targets, const Epilogue *epilogue, int sms, bool weight_nk) {
+                             cudaStream_t stream, const OutTargets *targets, const Epilogue *epilogue, int sms, bool weight_nk, int64_t lda,
+                             const PrefillSplit &split, void *workspace) {
     using namespace prefill;
     using Cfg = Config<TM>;
     CUtensorMap map_w, map_a;
@@ -509,7 +636,7 @@ static int launch_prefill_tm(const void *a, const void *wq, const void *scale, v
                        : make_tensor_map_2d(&map_w, CU_TENSOR_MAP_DATA_TYPE_UINT8, wq, (uint64_t)N, (uint64_t)K, (uint64_t)N, TN, BK,
                                             CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B);
     if (rc != B200Q_OK) return rc;
-    rc = make_tensor_map_2d(&map_a, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, a, (uint64_t)K, (uint64_t)M, (uint64_t)K * 2, BK, TM,
+    rc = make_tensor_map_2d(&map_a, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, a, (uint64_t)K, (uint64_t)M, (uint64_t)lda * 2, BK, TM,
                             CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B);
     if (rc != B200Q_OK) return rc;
 
@@ -534,7 +661,10 @@ static int launch_prefill_tm(const void *a, const void *wq, const void *scale, v
     p.K = (int)K;
     p.n_tiles = (int)ceil_div(N, TN);
     p.m_tiles = (int)ceil_div(M, TM);
-    const int64_t total = (int64_t)p.n_tiles * p.m_tiles;
+    p.k_splits = split.k_splits;
+    p.kb_per_split = split.k_splits > 1 ? split.kb_per_split : (int)ceil_div(K, BK);
+    p.partial = split.k_splits > 1 ? reinterpret_cast<float *>(static_cast<unsigned char *>(workspace) + kSplitWorkspaceHead) : nullptr;
+    const int64_t total = (int64_t)p.n_tiles * p.m_tiles * p.k_splits;
     if (total > 2147483647LL) return set_error(B200Q_UNSUPPORTED, "qlinear: problem too large for the tile counter");
     const unsigned grid = (unsigned)(total < sms ? total : sms);
 
@@ -548,6 +678,19 @@ static int launch_prefill_tm(const void *a, const void *wq, const void *scale, v
         if (dev >= 0 && dev < 64) attr_set[dev] = true;
     }
     const bool fused = p.ep.bias != nullptr || p.ep.residual != nullptr || p.ep.act != kActNone;
+    if (p.k_splits > 1) {
+        // the splits write raw sums; the reduce kernel scales, applies the epilogue and delivers
+        if (weight_nk) {
+            qlinear_prefill_kn_kernel<TM, false, true><<<grid, THREADS, Cfg::SMEM_BYTES, stream>>>(map_w, map_a, p);
+        } else {
+            qlinear_prefill_kn_kernel<TM, false, false><<<grid, THREADS, Cfg::SMEM_BYTES, stream>>>(map_w, map_a, p);
+        }
+        B200Q_CHECK_LAUNCH("qlinear_prefill_kn_kernel");
+        const int64_t threads = M * (N / 8);
+        qlinear_prefill_reduce_kernel<<<(unsigned)ceil_div(threads, 256), 256, 0, stream>>>(p.partial, p.scale, p.out, p.ep, (int)M, (int)N, p.k_splits);
+        B200Q_CHECK_LAUNCH("qlinear_prefill_reduce_kernel");
+        return B200Q_OK;
+    }
     if (weight_nk) {
         if (fused) return set_error(B200Q_UNSUPPORTED, "qlinear: the fused epilogue is served for [K, N] weights");
         qlinear_prefill_kn_kernel<TM, false, true><<<grid, THREADS, Cfg::SMEM_BYTES, stream>>>(map_w, map_a, p);
@@ -565,22 +708,22 @@ bool prefill_nk_supported(const void *a, const void *wq, int64_t N, int64_t K) {
 }
 
 int launch_prefill_kn(const void *a, const void *wq, const void *scale, void *c, int64_t M, int64_t N, int64_t K,
-                      cudaStream_t stream, const OutTargets *targets, const Epilogue *epilogue, bool weight_nk) {
+                      cudaStream_t stream, const OutTargets *targets, const Epilogue *epilogue, bool weight_nk, int64_t lda,
+                      void *workspace, size_t workspace_bytes) {
+    if (lda <= 0) lda = K;
     int sms = sm_count();
     if (sms <= 0) sms = 148;
-    int tm = choose_tile_m(M, N, sms);
-    if (tm == 256 && targets != nullptr && targets->count > 1) {
-        // Peer delivery: a tile's rows leave for the other GPUs only when the tile is finished, so with tall tiles the
-        // links idle during the first tile and carry everything in what is left.  When the bytes that have to leave
-        // (at about 700 GB/s) weigh as much as the product itself, short tiles start the delivery early and spread
-        // it over the whole launch; that is worth more than the tall tiles' better tensor-core rate.
-        const double compute_us = 2.0 * (double)M * (double)N * (double)K / 900e6;
-        const double delivery_us = (double)M * (double)N * 2.0 * (double)(targets->count - 1) / 700e3;
-        if (delivery_us > 0.6 * compute_us) tm = 64;
+    // K is split only when the caller brought the scratch for it (the entry points without a workspace do not split).
+    PrefillSplit split = plan_prefill_split(M, N, K);
+    if (split.k_splits > 1 && (workspace == nullptr || workspace_bytes < split.workspace_bytes)) split = PrefillSplit();
+    if (split.k_splits > 1 && targets != nullptr && targets->multicast && epilogue != nullptr && epilogue->act == kActSiluMul) split = PrefillSplit();
+    if (split.k_splits > 1) {
+        return launch_prefill_tm<256>(a, wq, scale, c, M, N, K, stream, targets, epilogue, sms, weight_nk, lda, split, workspace);
     }
+    const int tm = choose_tile_m(M, N, sms);
     switch (tm) {
-        case 64: return launch_prefill_tm<64>(a, wq, scale, c, M, N, K, stream, targets, epilogue, sms, weight_nk);
-        default: return launch_prefill_tm<256>(a, wq, scale, c, M, N, K, stream, targets, epilogue, sms, weight_nk);
+        case 64: return launch_prefill_tm<64>(a, wq, scale, c, M, N, K, stream, targets, epilogue, sms, weight_nk, lda, split, workspace);
+        default: return launch_prefill_tm<256>(a, wq, scale, c, M, N, K, stream, targets, epilogue, sms, weight_nk, lda, split, workspace);
     }
 }
 

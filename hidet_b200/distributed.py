@@ -80,26 +80,28 @@ class PeerOutput:
         import torch.distributed._symmetric_memory as symm_mem
 
         group = group if group is not None else dist.group.WORLD
-        self.buffers, self.handles, self.ptr_tables = [], [], []
+        self.buffers, self.handles, self.ptr_tables, self.multicast_ptrs = [], [], [], []
         for _ in range(2):
             buf = symm_mem.empty((rows, cols), dtype=torch.float16, device=device)
             handle = symm_mem.rendezvous(buf, group)
             self.buffers.append(buf)
             self.handles.append(handle)
             self.ptr_tables.append([int(p) for p in handle.buffer_ptrs])
+            # non-zero when the allocation is also bound to an NVLink multicast object (NVSwitch systems)
+            self.multicast_ptrs.append(int(getattr(handle, 'multicast_ptr', 0) or 0))
         self.turn = 0
 
     def release(self) -> None:
         """Drops the buffers, handles and pointer tables.  Call it on every rank before the process group is
         destroyed (and before a rank exits), while no kernel that stores to a peer is in flight: memory that
         is still peer-mapped when its owner goes away faults the GPUs that map it."""
-        self.buffers, self.handles, self.ptr_tables = [], [], []
+        self.buffers, self.handles, self.ptr_tables, self.multicast_ptrs = [], [], [], []
 
     def next(self):
-        """(local buffer, table of every rank's pointer to its copy, handle) for the next result."""
+        """(local buffer, table of every rank's pointer to its copy, handle, multicast pointer or 0) for the next result."""
         i = self.turn
         self.turn ^= 1
-        return self.buffers[i], self.ptr_tables[i], self.handles[i]
+        return self.buffers[i], self.ptr_tables[i], self.handles[i], self.multicast_ptrs[i]
 
 
 class ColumnParallelQuantLinear:
@@ -112,12 +114,16 @@ class ColumnParallelQuantLinear:
                    (rank-major, as the reference's all-gather op) and one copy puts them side by side;
     gather='p2p'   every rank's [M, N] output is peer-mapped on all ranks (symmetric memory), and the kernel's
                    epilogue stores its columns straight into every rank's output over NVLink, tile by tile
-                   while the rest of the product is still being computed (b200q_qlinear_f16_i8_to_peers).
+                   while the rest of the product is still being computed (b200q_qlinear_f16_i8_to_peers); where the
+                   outputs are also bound to an NVLink multicast object, large M stores once to the multicast
+                   address and the switch delivers to all ranks (b200q_qlinear_f16_i8_to_multicast).
                    One cross-rank barrier on the stream follows: no staging buffer, no reshuffle, no
                    collective launch.
     """
 
-    def __init__(self, wq_shard: torch.Tensor, scale_shard: torch.Tensor, group=None, gather: str = 'nccl'):
+    MULTICAST_MIN_ROWS = 33   # what the large-M kernel serves
+
+    def __init__(self, wq_shard: torch.Tensor, scale_shard: torch.Tensor, group=None, gather: str = 'nccl', multicast: bool = True):
         if wq_shard.dtype != torch.int8 or wq_shard.dim() != 2:
             raise ValueError('expect an int8 [K, N/g] weight shard')
         if gather not in ('nccl', 'p2p'):
@@ -126,6 +132,7 @@ class ColumnParallelQuantLinear:
         self.scale = scale_shard.contiguous()
         self.group = group
         self.gather = gather
+        self.multicast = multicast   # use the NVLink multicast mapping of the outputs for large M where there is one
         self.world = dist.get_world_size(group)
         self.rank = dist.get_rank(group)
         if gather == 'p2p' and self.world > 8:
@@ -134,11 +141,11 @@ class ColumnParallelQuantLinear:
         self._peer_outputs = {}
 
     @classmethod
-    def from_weight_shard(cls, w_shard: torch.Tensor, group=None, gather: str = 'nccl'):
+    def from_weight_shard(cls, w_shard: torch.Tensor, group=None, gather: str = 'nccl', multicast: bool = True):
         from .quant import symmetric_quantize
 
         wq, scale = symmetric_quantize(w_shard, 'int8', dims=0)
-        return cls(wq, scale, group, gather)
+        return cls(wq, scale, group, gather, multicast)
 
     def share_outputs_with(self, other: 'ColumnParallelQuantLinear') -> None:
         """Use `other`'s peer-mapped output buffers (layers of equal width that run one after the
@@ -180,7 +187,7 @@ class ColumnParallelQuantLinear:
         key = (rows, x.device)
         if key not in self._peer_outputs:
             self._peer_outputs[key] = PeerOutput(rows, n, x.device, self.group)
-        out, ptrs, handle = self._peer_outputs[key].next()
+        out, ptrs, handle, multicast_ptr = self._peer_outputs[key].next()
         x = x.contiguous()
         c0 = self.rank * n_local
         qlinear = ffi.func('b200q_qlinear_f16_i8_to_peers')
@@ -188,9 +195,14 @@ class ColumnParallelQuantLinear:
             ws_bytes = ffi.func('b200q_qlinear_workspace_bytes')(rows, n_local, k, ffi.LAYOUT_KN)
             ws_ptr, ws_size = workspaces.get(x.device, ws_bytes)
             main = torch.cuda.current_stream(x.device)
-            table = (ctypes.c_void_p * self.world)(*ptrs)
-            qlinear(x.data_ptr(), self.wq.data_ptr(), self.scale.data_ptr(), table, self.world, n, c0, rows, n_local, k,
-                    ws_ptr, ws_size, main.cuda_stream)
+            if multicast_ptr and self.multicast and rows >= self.MULTICAST_MIN_ROWS:
+                # large M: every 16 bytes leave this GPU once and the switch delivers them to all ranks
+                ffi.func('b200q_qlinear_f16_i8_to_multicast')(x.data_ptr(), self.wq.data_ptr(), self.scale.data_ptr(), multicast_ptr, n, c0,
+                                                            rows, n_local, k, ws_ptr, ws_size, main.cuda_stream)
+            else:
+                table = (ctypes.c_void_p * self.world)(*ptrs)
+                qlinear(x.data_ptr(), self.wq.data_ptr(), self.scale.data_ptr(), table, self.world, n, c0, rows, n_local, k,
+                        ws_ptr, ws_size, main.cuda_stream)
             handle.barrier(channel=0)  # on the current stream: every rank's columns have landed everywhere
         return out.view(lead + (n,))
 

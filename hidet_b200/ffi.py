@@ -154,6 +154,11 @@ SIGNATURES = {
         c_int,
         True,
     ),
+    'b200q_qlinear_f16_i8_to_multicast': (
+        [c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64, c_int64, c_int64, c_void_p, c_size_t, c_void_p],
+        c_int,
+        True,
+    ),
     'b200q_push_columns': ([c_void_p, c_void_p, c_int, c_int64, c_int64, c_int64, c_int64, c_void_p], c_int, True),
     'b200q_qlinear_static_scratch_bytes': ([], c_size_t, False),
     'b200q_qlinear_f16_i8_static': ([c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64, c_int, c_void_p], c_int, True),

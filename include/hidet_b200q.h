@@ -221,6 +221,19 @@ B200Q_API int b200q_qlinear_f16_i8_to_peers(const void *a, const void *wq, const
                                             size_t workspace_bytes, void *stream);
 
 /*
+ * The same for large M through an NVLink multicast address: `multicast_dst` maps the [M, ldc] output buffers of all
+ * ranks of the group at once (a multicast object over symmetric allocations, e.g. the multicast pointer of a
+ * torch symmetric-memory handle), and the large-M kernel's epilogue stores every 16 bytes once with multimem.st;
+ * the switch delivers them to every GPU, this one included.  The bytes that leave this GPU are 1 / (ranks - 1) of
+ * what b200q_qlinear_f16_i8_to_peers sends.  M >= 33 and operands the large-M kernel accepts, else
+ * B200Q_UNSUPPORTED (use b200q_qlinear_f16_i8_to_peers); workspace as for b200q_qlinear_f16_i8.  The caller orders the ranks
+ * afterwards, as above.  No counterpart in the reference beyond the all-gather op named above.
+ */
+B200Q_API int b200q_qlinear_f16_i8_to_multicast(const void *a, const void *wq, const void *scale, void *multicast_dst, int64_t ldc,
+                                                int64_t col_offset, int64_t M, int64_t N, int64_t K, void *workspace, size_t workspace_bytes,
+                                                void *stream);
+
+/*
  * Delivery by copies instead of epilogue stores (an alternative, not what the layer uses): copies columns
  * [col_offset, col_offset + cols) of the fp16 matrix src[rows, ld] into the same place of every
  * dst[i][rows, ld] (pointers valid on this device, peer-mapped for other GPUs; an entry equal to src

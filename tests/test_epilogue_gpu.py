@@ -20,9 +20,10 @@ from hidet_b200.quant import interleave_gate_up
 
 pytestmark = pytest.mark.gpu
 
-# small-M kernel: cluster split, one CTA per tile, splits through the workspace; large-M kernel: short and tall tiles
+# small-M kernel: cluster split, one CTA per tile, splits through the workspace; large-M kernel: short and tall tiles,
+# and (the last two) K split over several CTAs per tile with the epilogue in the reduce kernel
 SHAPES = [(1, 4096, 4096), (4, 1024, 512), (16, 4096, 1024), (3, 512, 19008), (4, 16384, 256), (12, 2048, 16), (40, 512, 256),
-          (300, 1024, 768), (2048, 512, 1024)]
+          (300, 1024, 768), (2048, 512, 1024), (300, 4096, 1024), (100, 8192, 528)]
 
 
 def float64_sums(a, wq, scale):

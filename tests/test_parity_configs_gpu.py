@@ -188,3 +188,25 @@ def test_quantize_then_linear_inside_one_captured_graph():
         wq_w, scale_w = hidet_b200.symmetric_quantize(w, 'int8', dims=0)
         assert torch.equal(c, hidet_b200.symmetric_quant_matmul(a, wq_w, scale_w))
     assert ffi.func('b200q_check_status')() == ffi.OK
+
+
+@pytest.mark.parametrize('m,k,n,layout', [(256, 8192, 3584, 'KN'), (300, 4096, 1024, 'KN'), (300, 4096, 1024, 'NK'), (65, 2048, 144, 'KN')])
+def test_large_m_kernel_with_k_split_over_ctas(m, k, n, layout):
+    """A narrow problem at a few hundred rows (an eight-way column shard of the 70B layer at M = 256 is the first
+    shape) would leave most SMs without a tile: K is split over several CTAs per tile, raw fp32 sums meet in the
+    workspace and a second kernel finishes.  Same yardsticks as everywhere, and the same bits on every run."""
+    assert ffi.func('b200q_qlinear_workspace_bytes')(m, n, k, 0) > 65536 * 4 + 2 * m * n * 4 - 1   # the split plan is on
+    w = seeded_weight(k, n, seed=k + n)
+    wq, scale = oracle.symmetric_quantize(w, 'int8', 0)
+    a = seeded_activation(m, k, seed=m)
+    a_t, scale_t = torch.from_numpy(a).cuda(), torch.from_numpy(scale).cuda()
+    wq_t = torch.from_numpy(wq).cuda() if layout == 'KN' else torch.from_numpy(np.ascontiguousarray(wq.T)).cuda()
+    c = hidet_b200.symmetric_quant_matmul(a_t, wq_t, scale_t, weight_layout=layout)
+    assert torch.equal(c, hidet_b200.symmetric_quant_matmul(a_t, wq_t, scale_t, weight_layout=layout))
+    exact = a.astype(np.float64) @ (wq.astype(np.float64) * scale.astype(np.float64))
+    top = np.abs(exact).max()
+    got = c.float().cpu().numpy()
+    assert np.abs(got - exact).max() <= 1e-3 * top
+    want = oracle.symmetric_quant_matmul(a, wq, scale)
+    assert np.abs(got - want.astype(np.float64)).max() <= 1e-2 * top
+    assert ffi.func('b200q_check_status')() == ffi.OK
