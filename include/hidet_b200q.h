@@ -263,7 +263,9 @@ B200Q_API size_t b200q_qlinear_static_scratch_bytes(void);
  * library's device image, held by every GPU that loads the library until the process exits.
  *
  *   - same operands and result as b200q_qlinear_f16_i8 with w_layout = B200Q_LAYOUT_KN; operands must
- *     have 16-byte aligned bases and rows (N % 16 == 0, K % 8 == 0);
+ *     have 16-byte aligned bases and rows (N % 16 == 0, K % 8 == 0).  (One exception to "same result": a
+ *     narrow weight at M >= 33, where b200q_qlinear_f16_i8 splits K over several CTAs per tile and needs MBs
+ *     of scratch for it, is computed here without the split: same value, fp32 sums grouped differently);
  *   - a problem whose scratch requirement (b200q_qlinear_workspace_bytes) exceeds the built-in array
  *     is refused with B200Q_WORKSPACE_TOO_SMALL and a message naming both sizes (most shapes need no
  *     scratch; narrow, deep weights with 16 or more activation rows can exceed the array);
