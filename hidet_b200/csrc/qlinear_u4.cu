@@ -26,7 +26,6 @@ constexpr int COLS_PER_THREAD = 8;   // one 32-bit word of packed codes
 constexpr int WORDS_X = 32;          // threads along N: a warp covers 256 columns
 constexpr int K_SLICES = 8;          // warps of a CTA, each on its own k rows
 constexpr int THREADS = WORDS_X * K_SLICES;
-constexpr int MT = 4;                // activation rows per pass
 // The head of a workspace is where the int8 kernels keep their arrival counters (all-zero between calls); this op
 // leaves it alone, so one workspace can serve both.
 constexpr size_t kReservedHead = (size_t)65536 * 4;
@@ -47,6 +46,10 @@ __device__ __forceinline__ void unpack8(uint32_t w, float (&v)[8]) {
     for (int c = 0; c < 8; ++c) v[c] = __uint_as_float(((w >> (4 * c)) & 0xFu) | 0x4B000000u) - 8388608.0f;
 }
 
+// MT: activation rows per pass (1, 2 or 4: the smallest that covers M, so that a single row costs a single row's
+// multiplications).  The k loop is taken four rows at a time with all loads issued first: a thread has only a few
+// dozen rows, and one load per iteration would leave it waiting for memory most of the time.
+template <int MT>
 __global__ void __launch_bounds__(THREADS) qlinear_u4_partial_kernel(const Params p) {
     __shared__ float red[K_SLICES][MT][WORDS_X * COLS_PER_THREAD + 8];
     const int word = blockIdx.x * WORDS_X + threadIdx.x;  // which group of eight columns
@@ -58,6 +61,7 @@ __global__ void __launch_bounds__(THREADS) qlinear_u4_partial_kernel(const Param
     const int words_per_row = p.N / COLS_PER_THREAD;
     const bool in = n0 < p.N;
     float *out = p.partial + (size_t)split * p.M * p.N;
+    constexpr int UNROLL = 4;
 
     for (int m0 = 0; m0 < p.M; m0 += MT) {
         float acc[MT][8];
@@ -66,6 +70,9 @@ __global__ void __launch_bounds__(THREADS) qlinear_u4_partial_kernel(const Param
 #pragma unroll
             for (int c = 0; c < 8; ++c) acc[m][c] = 0.0f;
         if (in) {
+            const __half *arow[MT];
+#pragma unroll
+            for (int m = 0; m < MT; ++m) arow[m] = p.a + (size_t)min(m0 + m, p.M - 1) * p.K;  // rows beyond M repeat the last one and are not stored
             for (int g0 = k_begin; g0 < k_end; g0 += p.G) {
                 float gs[MT][8], asum[MT];
 #pragma unroll
@@ -75,15 +82,27 @@ __global__ void __launch_bounds__(THREADS) qlinear_u4_partial_kernel(const Param
                     for (int c = 0; c < 8; ++c) gs[m][c] = 0.0f;
                 }
                 const int g_end = min(k_end, g0 + p.G);
-                for (int k = g0 + slice; k < g_end; k += K_SLICES) {
-                    float v[8];
-                    unpack8(__ldg(p.q + (size_t)k * words_per_row + word), v);
+                for (int kb = g0 + slice; kb < g_end; kb += UNROLL * K_SLICES) {
+                    uint32_t w[UNROLL];
+                    float av[UNROLL][MT];
 #pragma unroll
-                    for (int m = 0; m < MT; ++m) {
-                        const float av = m0 + m < p.M ? __half2float(__ldg(p.a + (size_t)(m0 + m) * p.K + k)) : 0.0f;
-                        asum[m] += av;
+                    for (int u = 0; u < UNROLL; ++u) {
+                        const int k = kb + u * K_SLICES;
+                        const bool ok = k < g_end;
+                        w[u] = ok ? __ldg(p.q + (size_t)k * words_per_row + word) : 0u;
 #pragma unroll
-                        for (int c = 0; c < 8; ++c) gs[m][c] = fmaf(av, v[c], gs[m][c]);
+                        for (int m = 0; m < MT; ++m) av[u][m] = ok ? __half2float(__ldg(arow[m] + k)) : 0.0f;
+                    }
+#pragma unroll
+                    for (int u = 0; u < UNROLL; ++u) {
+                        float v[8];
+                        unpack8(w[u], v);
+#pragma unroll
+                        for (int m = 0; m < MT; ++m) {
+                            asum[m] += av[u][m];
+#pragma unroll
+                            for (int c = 0; c < 8; ++c) gs[m][c] = fmaf(av[u][m], v[c], gs[m][c]);
+                        }
                     }
                 }
                 const size_t grow = (size_t)(g0 / p.G) * p.N + n0;
@@ -156,7 +175,7 @@ Plan plan(int64_t M, int64_t N, int64_t K, int64_t G) {
     if (sms <= 0) sms = 148;
     const int64_t col_blocks = ceil_div(N, (int64_t)WORDS_X * COLS_PER_THREAD);
     const int64_t groups = ceil_div(K, G);
-    int64_t splits = ceil_div((int64_t)2 * sms, col_blocks);  // two CTAs per SM
+    int64_t splits = ceil_div((int64_t)4 * sms, col_blocks);  // four CTAs per SM: the loads of many rows in flight
     if (splits > groups) splits = groups;
     if (splits < 1) splits = 1;
     Plan pl;
@@ -214,7 +233,14 @@ B200Q_API int b200q_qlinear_f16_u4(const void *a, const void *q, const void *sca
     p.G = (int)group_size;
     p.k_per_split = pl.k_per_split;
     const dim3 grid((unsigned)ceil_div(N, (int64_t)u4::WORDS_X * u4::COLS_PER_THREAD), (unsigned)pl.splits, 1);
-    u4::qlinear_u4_partial_kernel<<<grid, dim3(u4::WORDS_X, u4::K_SLICES, 1), 0, s>>>(p);
+    const dim3 block(u4::WORDS_X, u4::K_SLICES, 1);
+    if (M == 1) {
+        u4::qlinear_u4_partial_kernel<1><<<grid, block, 0, s>>>(p);
+    } else if (M == 2) {
+        u4::qlinear_u4_partial_kernel<2><<<grid, block, 0, s>>>(p);
+    } else {
+        u4::qlinear_u4_partial_kernel<4><<<grid, block, 0, s>>>(p);
+    }
     B200Q_CHECK_LAUNCH("qlinear_u4_partial_kernel");
     const int64_t mn = M * N;
     u4::qlinear_u4_reduce_kernel<<<(unsigned)ceil_div(mn, 256), 256, 0, s>>>(p.partial, static_cast<__half *>(c), mn, pl.splits);
