@@ -47,7 +47,7 @@ __device__ __forceinline__ void unpack8(uint32_t w, float (&v)[8]) {
 }
 
 // MT: activation rows per pass (1, 2 or 4: the smallest that covers M, so that a single row costs a single row's
-// multiplications).  The k loop is taken four rows at a time with all loads issued first: a thread has only a few
+// multiplications).  The k loop is taken 4 to 16 rows at a time with all loads issued first: a thread has only a few
 // dozen rows, and one load per iteration would leave it waiting for memory most of the time.
 template <int MT>
 __global__ void __launch_bounds__(THREADS) qlinear_u4_partial_kernel(const Params p) {
@@ -61,7 +61,7 @@ __global__ void __launch_bounds__(THREADS) qlinear_u4_partial_kernel(const Param
     const int words_per_row = p.N / COLS_PER_THREAD;
     const bool in = n0 < p.N;
     float *out = p.partial + (size_t)split * p.M * p.N;
-    constexpr int UNROLL = 4;
+    constexpr int UNROLL = MT == 1 ? 16 : (MT == 2 ? 8 : 4);  // rows whose loads are in flight together
 
     for (int m0 = 0; m0 < p.M; m0 += MT) {
         float acc[MT][8];
