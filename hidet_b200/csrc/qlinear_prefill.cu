@@ -8,11 +8,13 @@
 // bandwidth headroom that the opposite assignment would not.
 //
 // One persistent CTA per SM, fourteen warps:
-//   warp 12     TMA producer: per 64-k stage one int8 tile [64 k][128 n] (plain layout, its own short
+//   warp 12     TMA producer: per 64-k stage one int8 tile [64 k][128 n] (128B swizzle, its own short
 //               ring) and one activation tile [TM m][64 k] f16 (128B swizzle = K-major MMA operand as is);
 //               TM = 256, or 64 when that fills more SMs
-//   warps 4-11  converters: int8 -> exact f16 in registers, written as the MN-major, 128B-swizzled MMA
-//               operand ([2 column blocks][8 k-groups][8 k][64 n]), then a proxy fence and an mbarrier
+//   warps 4-11  converters: transposing matrix loads of the int8 tile (four consecutive k of one column per
+//               register), int8 -> exact f16 in registers, written as the K-major, 128B-swizzled MMA
+//               operand ([128 n][64 k], the same as for weights stored [N, K]) with 8-byte stores that
+//               touch every bank once, then a proxy fence and an mbarrier
 //   warp 13     MMA issuer (one lane): four K=16 MMAs per stage into one of two 256-column TMEM
 //               accumulators; tcgen05.commit frees the stage / publishes the accumulator
 //   warps 0-3   epilogue: tcgen05.ld of the accumulator (lane = weight column n, column = row m),
@@ -64,11 +66,9 @@ struct Config {
     static constexpr int MAIN_BYTES = ACT_BYTES + WF_BYTES;
     static constexpr int SMEM_BYTES = STAGES * MAIN_BYTES + RAW_SLOTS * RAW_BYTES + STAGING_BYTES + 1024;  // + alignment slack
     static constexpr uint32_t TMEM_COLS = 2 * TM;            // two accumulators of TM fp32 columns (a power of two >= 32)
-    // tcgen05 instruction descriptor, kind::f16: D = f32, A = B = f16, A is MN-major, B is K-major,
+    // tcgen05 instruction descriptor, kind::f16: D = f32, A = B = f16, both K-major,
     // N = TM (bits 17..22 hold N / 8), M = 128 (bits 24..28 hold M / 16).
-    static constexpr uint32_t kInstrDesc = (1u << 4) | (1u << 15) | ((uint32_t)(TM >> 3) << 17) | ((uint32_t)(TN >> 4) << 24);
-    // the same with A K-major (bit 15 clear): a weight stored [N, K] is converted row by row
-    static constexpr uint32_t kInstrDescNK = (1u << 4) | ((uint32_t)(TM >> 3) << 17) | ((uint32_t)(TN >> 4) << 24);
+    static constexpr uint32_t kInstrDesc = (1u << 4) | ((uint32_t)(TM >> 3) << 17) | ((uint32_t)(TN >> 4) << 24);
 };
 
 // Shared-memory matrix descriptor: start address, leading / stride byte offsets (all in 16-byte
@@ -120,6 +120,16 @@ __device__ __forceinline__ void tmem_ld_32x32(uint32_t taddr, uint32_t (&v)[32])
 }
 __device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 
+// Two 16 x 16 byte tiles, transposed on the way to registers.  Lanes 0-15 give the addresses of the 16 rows (16 bytes
+// each) of the first tile, lanes 16-31 those of the second.  With a tile stored as [k][column], lane (g = lane / 4,
+// t = lane % 4) receives, for tile i, in r[2i] the bytes (k = 4t .. 4t+3, column g) and in r[2i+1] the bytes
+// (k = 4t .. 4t+3, column g + 8).
+__device__ __forceinline__ void ldmatrix_x2_trans_b8(uint32_t (&r)[4], uint32_t addr) {
+    asm volatile("ldmatrix.sync.aligned.m16n16.x2.trans.shared.b8 {%0, %1, %2, %3}, [%4];" : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
+}
+__device__ __forceinline__ void sts64(uint32_t addr, uint32_t a, uint32_t b) {
+    asm volatile("st.shared.v2.b32 [%0], {%1, %2};" ::"r"(addr), "r"(a), "r"(b) : "memory");
+}
 __device__ __forceinline__ uint4 lds128(uint32_t addr) {
     uint4 v;
     asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr));
@@ -313,12 +323,11 @@ __global__ void __launch_bounds__(THREADS, 1) qlinear_prefill_kn_kernel(const __
                     tc_fence_after_sync();
 #pragma unroll
                     for (int ks = 0; ks < BK / 16; ++ks) {
-                        // A: MN-major f16 weights, column blocks 8192 B apart, 8-k groups 1024 B apart; K = 16 is two groups.
-                        // ([N, K] weights: K-major like B.)
-                        const uint64_t da = NK ? smem_desc(wf_addr(s) + ks * 32, 16, 1024) : smem_desc(wf_addr(s) + ks * 2048, 8192, 1024);
+                        // A: K-major f16 weights (whichever way the int8 weight is stored), like B
+                        const uint64_t da = smem_desc(wf_addr(s) + ks * 32, 16, 1024);
                         // B: K-major activations, 8-row groups 1024 B apart; K = 16 is 32 bytes along the swizzled row.
                         const uint64_t db = smem_desc(act_addr(s) + ks * 32, 16, 1024);
-                        umma_f16(d_addr, da, db, NK ? Cfg::kInstrDescNK : Cfg::kInstrDesc, (kb > kb_begin || ks > 0) ? 1u : 0u);
+                        umma_f16(d_addr, da, db, Cfg::kInstrDesc, (kb > kb_begin || ks > 0) ? 1u : 0u);
                     }
                     umma_commit(smem_u32(&slot_free[s]));
                 }
@@ -332,14 +341,8 @@ __global__ void __launch_bounds__(THREADS, 1) qlinear_prefill_kn_kernel(const __
         // ---------------- converters ----------------
         const int cw = warp - CONV_WARP0;
         const int group = cw % CONV_GROUPS;            // this warp's group converts stages group, group + CONV_GROUPS, ...
+        const int gw = cw / CONV_GROUPS;               // this warp inside its group
         const int ct = (cw / CONV_GROUPS) * 32 + lane; // 0 .. 32 * GROUP_WARPS - 1 inside the group
-        const int ci = ct & 7;                         // 16-byte chunk of an int8 row: columns 16 ci .. 16 ci + 15
-        const int rb = ct >> 3;                        // row inside a pass of CONV_ROWS rows
-        // f16 chunks (8 columns each) 2 ci and 2 ci + 1 of the 16 per row; chunk c lives in column block
-        // c / 8 at slot (c % 8) ^ (k % 8) of its 128-byte row.  Half of the threads write the odd chunk
-        // first so that the eight threads of a row hit eight different bank groups.
-        const int c_first = (ci & 4) ? 2 * ci + 1 : 2 * ci;
-        const int c_second = (ci & 4) ? 2 * ci : 2 * ci + 1;
         uint32_t i = 0;
         bool ok = true;
         for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
@@ -356,13 +359,12 @@ __global__ void __launch_bounds__(THREADS, 1) qlinear_prefill_kn_kernel(const __
                     break;
                 }
                 const uint32_t raw = raw_addr(r), wf = wf_addr(s);
-                uint4 v[BK / CONV_ROWS];
-#pragma unroll
-                for (int pass = 0; pass < BK / CONV_ROWS; ++pass)
-                    v[pass] = NK ? lds128(raw + (pass * (32 * GROUP_WARPS) + ct) * 16) : lds128(raw + (pass * CONV_ROWS + rb) * 128 + ci * 16);
-                __syncwarp();
-                if (lane == 0) mbar_arrive(smem_u32(&raw_empty[r]));  // the int8 tile is in registers
                 if (NK) {
+                    uint4 v[BK / CONV_ROWS];
+#pragma unroll
+                    for (int pass = 0; pass < BK / CONV_ROWS; ++pass) v[pass] = lds128(raw + (pass * (32 * GROUP_WARPS) + ct) * 16);
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(smem_u32(&raw_empty[r]));  // the int8 tile is in registers
                     // 16-byte piece `id` of the tile is 16 k of weight row id / 4: two 8-k chunks of that row's 128 f16 bytes
 #pragma unroll
                     for (int pass = 0; pass < BK / CONV_ROWS; ++pass) {
@@ -377,25 +379,35 @@ __global__ void __launch_bounds__(THREADS, 1) qlinear_prefill_kn_kernel(const __
                         sts128(row + ((c2 ^ (n & 7)) << 4), h[0], h[1], h[2], h[3]);
                         sts128(row + (((c2 + 1) ^ (n & 7)) << 4), h[4], h[5], h[6], h[7]);
                     }
-                } else
+                } else {
+                    // [K, N] weights: the int8 tile is [64 k][128 n], 128B-swizzled.  Transposing matrix loads hand every
+                    // lane four consecutive k of one column per register (column g / g + 8 of a 16-column block, k = 4t ..
+                    // 4t + 3 of a 16-row block); converted, that is 8 bytes of the column's row in the K-major operand
+                    // (rows of 64 k = 128 bytes, 16-byte chunk c of row n at chunk c ^ (n % 8)): the same operand as for
+                    // [N, K] weights, and stores that touch every bank once.
+                    constexpr int PAIRS = 4 / GROUP_WARPS;  // pairs of 16-column blocks per warp (the group covers 8 blocks)
+                    uint32_t q[PAIRS][4][4];
 #pragma unroll
-                for (int pass = 0; pass < BK / CONV_ROWS; ++pass) {
-                    const int k = pass * CONV_ROWS + rb;
-                    uint32_t h[8];
-                    cvt_s8x4_to_f16_pairs(v[pass].x, h[0], h[1]);
-                    cvt_s8x4_to_f16_pairs(v[pass].y, h[2], h[3]);
-                    cvt_s8x4_to_f16_pairs(v[pass].z, h[4], h[5]);
-                    cvt_s8x4_to_f16_pairs(v[pass].w, h[6], h[7]);
-                    const uint32_t row = wf + (k >> 3) * 1024 + (k & 7) * 128;
-                    const uint32_t a_first = row + (c_first >> 3) * 8192 + (((c_first & 7) ^ (k & 7)) << 4);
-                    const uint32_t a_second = row + (c_second >> 3) * 8192 + (((c_second & 7) ^ (k & 7)) << 4);
-                    if (ci & 4) {
-                        sts128(a_first, h[4], h[5], h[6], h[7]);
-                        sts128(a_second, h[0], h[1], h[2], h[3]);
-                    } else {
-                        sts128(a_first, h[0], h[1], h[2], h[3]);
-                        sts128(a_second, h[4], h[5], h[6], h[7]);
-                    }
+                    for (int pr = 0; pr < PAIRS; ++pr)
+#pragma unroll
+                        for (int ks = 0; ks < 4; ++ks) {
+                            const int chunk = 2 * (gw * PAIRS + pr) + (lane >> 4);  // 16-column block addressed by this lane
+                            ldmatrix_x2_trans_b8(q[pr][ks], raw + (ks * 16 + (lane & 15)) * 128 + ((chunk ^ (lane & 7)) << 4));
+                        }
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(smem_u32(&raw_empty[r]));  // the int8 tile is in registers
+                    const int g = lane >> 2, t = lane & 3;
+#pragma unroll
+                    for (int pr = 0; pr < PAIRS; ++pr)
+#pragma unroll
+                        for (int ks = 0; ks < 4; ++ks)
+#pragma unroll
+                            for (int i = 0; i < 4; ++i) {
+                                const int n = 32 * (gw * PAIRS + pr) + 8 * i + g;  // register i: columns g, g + 8 of the first block, then of the second
+                                uint32_t lo, hi;
+                                cvt_s8x4_to_f16_pairs(q[pr][ks][i], lo, hi);
+                                sts64(wf + n * 128 + (((2 * ks + (t >> 1)) ^ (n & 7)) << 4) + 8 * (t & 1), lo, hi);
+                            }
                 }
                 fence_proxy_async_smem();  // the tensor core reads these bytes through the async proxy
                 __syncwarp();
@@ -634,7 +646,7 @@ static int launch_prefill_tm(const void *a, const void *wq, const void *scale, v
     int rc = weight_nk ? make_tensor_map_2d(&map_w, CU_TENSOR_MAP_DATA_TYPE_UINT8, wq, (uint64_t)K, (uint64_t)N, (uint64_t)K, BK, TN,
                                             CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B)
                        : make_tensor_map_2d(&map_w, CU_TENSOR_MAP_DATA_TYPE_UINT8, wq, (uint64_t)N, (uint64_t)K, (uint64_t)N, TN, BK,
-                                            CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B);
+                                            CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B);
     if (rc != B200Q_OK) return rc;
     rc = make_tensor_map_2d(&map_a, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, a, (uint64_t)K, (uint64_t)M, (uint64_t)lda * 2, BK, TM,
                             CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B);
