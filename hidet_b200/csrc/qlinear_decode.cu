@@ -25,6 +25,8 @@
 // Replaces the generated mma.sync kernel of python/hidet/graph/ops/quant/matmul_f16_i8.py:136-485
 // (f16 accumulation, 64x128 tiles, no split-K by default) for M <= 16, and serves larger M by
 // tiling M over blockIdx.z.
+#include <atomic>
+
 #include "common.cuh"
 #include "qlinear.h"
 
@@ -642,17 +644,17 @@ int launch_decode_kn(const void *a, const void *wq, const void *scale, void *c, 
     const bool one_block = M - (int64_t)(pl.m_tiles - 1) * BM <= 8 && pl.m_tiles == 1;
     auto kernel = weight_nk ? (one_block ? qlinear_decode_kn_kernel<1, true> : qlinear_decode_kn_kernel<2, true>)
                             : (one_block ? qlinear_decode_kn_kernel<1, false> : qlinear_decode_kn_kernel<2, false>);
-    static bool attr_set[64] = {false};  // per device; a repeated set is harmless
+    static std::atomic<bool> attr_set[64];  // per device, zero-initialised; a repeated set by a racing thread is harmless
     int dev = 0;
     B200Q_CUDA_TRY(cudaGetDevice(&dev));
-    if (dev < 0 || dev >= 64 || !attr_set[dev]) {
+    if (dev < 0 || dev >= 64 || !attr_set[dev].load(std::memory_order_acquire)) {
         const void *all[4] = {reinterpret_cast<const void *>(qlinear_decode_kn_kernel<1, false>), reinterpret_cast<const void *>(qlinear_decode_kn_kernel<2, false>),
                               reinterpret_cast<const void *>(qlinear_decode_kn_kernel<1, true>), reinterpret_cast<const void *>(qlinear_decode_kn_kernel<2, true>)};
         for (const void *f : all) {
             B200Q_CUDA_TRY(cudaFuncSetAttribute(f, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
             B200Q_CUDA_TRY(cudaFuncSetAttribute(f, cudaFuncAttributeNonPortableClusterSizeAllowed, 1));
         }
-        if (dev >= 0 && dev < 64) attr_set[dev] = true;
+        if (dev >= 0 && dev < 64) attr_set[dev].store(true, std::memory_order_release);
     }
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3((unsigned)pl.n_tiles, (unsigned)pl.splits, (unsigned)pl.m_tiles);

@@ -33,6 +33,8 @@
 // Replaces, for large M, the generated mma.sync kernel of
 // python/hidet/graph/ops/quant/matmul_f16_i8.py:136-485 (f16 accumulation) and the separate sum over
 // split-K parts that follows it (python/hidet/graph/ops/quant/resolve.py:99).
+#include <atomic>
+
 #include "common.cuh"
 #include "qlinear.h"
 
@@ -680,14 +682,14 @@ static int launch_prefill_tm(const void *a, const void *wq, const void *scale, v
     if (total > 2147483647LL) return set_error(B200Q_UNSUPPORTED, "qlinear: problem too large for the tile counter");
     const unsigned grid = (unsigned)(total < sms ? total : sms);
 
-    static bool attr_set[64] = {false};  // per device and instantiation; a repeated set is harmless
+    static std::atomic<bool> attr_set[64];  // per device and instantiation, zero-initialised; a repeated set by a racing thread is harmless
     int dev = 0;
     B200Q_CUDA_TRY(cudaGetDevice(&dev));
-    if (dev < 0 || dev >= 64 || !attr_set[dev]) {
+    if (dev < 0 || dev >= 64 || !attr_set[dev].load(std::memory_order_acquire)) {
         B200Q_CUDA_TRY(cudaFuncSetAttribute(qlinear_prefill_kn_kernel<TM, false, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES));
         B200Q_CUDA_TRY(cudaFuncSetAttribute(qlinear_prefill_kn_kernel<TM, true, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES));
         B200Q_CUDA_TRY(cudaFuncSetAttribute(qlinear_prefill_kn_kernel<TM, false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES));
-        if (dev >= 0 && dev < 64) attr_set[dev] = true;
+        if (dev >= 0 && dev < 64) attr_set[dev].store(true, std::memory_order_release);
     }
     const bool fused = p.ep.bias != nullptr || p.ep.residual != nullptr || p.ep.act != kActNone;
     if (p.k_splits > 1) {
