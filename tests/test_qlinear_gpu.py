@@ -213,7 +213,7 @@ def _to_destinations(a, wq, scale, dsts, ldc, col0):
                                              ws_ptr, ws_size, torch.cuda.current_stream().cuda_stream)
 
 
-@pytest.mark.parametrize('m,k,n', [(1, 1024, 256), (16, 8192, 1792), (32, 512, 128), (300, 2048, 256), (40, 8192, 4096)])
+@pytest.mark.parametrize('m,k,n', [(1, 1024, 256), (16, 8192, 1792), (32, 512, 128), (300, 2048, 256), (40, 8192, 4096), (300, 4096, 1024)])
 def test_qlinear_into_a_column_range_of_wider_outputs(m, k, n):
     """The column-parallel entry point on one GPU: every destination gets the plain result in its columns and
     nothing outside them, from either kernel."""
@@ -230,6 +230,24 @@ def test_qlinear_into_a_column_range_of_wider_outputs(m, k, n):
         assert torch.equal(d[:, col0:col0 + n], want)
         assert bool((d[:, :col0] == -7.0).all()) and bool((d[:, col0 + n:] == -7.0).all())
     assert ffi.func('b200q_check_status')() == ffi.OK
+
+
+def test_multicast_entry_point_refuses_what_it_does_not_serve():
+    """The multicast delivery needs an NVLink multicast mapping, which one GPU does not have; what can be checked
+    here is that the entry point takes large M only and says where small M goes."""
+    f = ffi.func('b200q_qlinear_f16_i8_to_multicast')
+    a = torch.zeros(16, 512, dtype=torch.float16, device='cuda')
+    wq = torch.zeros(512, 128, dtype=torch.int8, device='cuda')
+    scale = torch.ones(128, dtype=torch.float16, device='cuda')
+    out = torch.zeros(16, 128, dtype=torch.float16, device='cuda')
+    stream = torch.cuda.current_stream().cuda_stream
+    with pytest.raises(ffi.BackendException, match='to_peers') as e:
+        f(a.data_ptr(), wq.data_ptr(), scale.data_ptr(), out.data_ptr(), 128, 0, 16, 128, 512, None, 0, stream)
+    assert e.value.status == ffi.UNSUPPORTED
+    with pytest.raises(ffi.BackendException, match='null destination'):
+        f(a.data_ptr(), wq.data_ptr(), scale.data_ptr(), None, 128, 0, 16, 128, 512, None, 0, stream)
+    with pytest.raises(ffi.BackendException, match='do not fit'):
+        f(a.data_ptr(), wq.data_ptr(), scale.data_ptr(), out.data_ptr(), 64, 0, 16, 128, 512, None, 0, stream)
 
 
 def test_push_columns_copies_one_column_range_and_nothing_else():
