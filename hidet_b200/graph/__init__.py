@@ -19,6 +19,7 @@ from .patterns import (
     SymmetricQuantizeMatmulFused,
     SymmetricEmbeddingQuantizePattern,
     QuantizedLinearEpilogueFusion,
+    QuantizedLinearConcat,
     quantized_matmul,
     quantized_linear_nk,
     quantized_embedding,

@@ -342,6 +342,63 @@ class QuantizedLinearEpilogueFusion(SubgraphRewriteRule):
         return count
 
 
+class QuantizedLinearConcat(SubgraphRewriteRule):
+    """Several plain quantized linears of the same input (the query / key / value projections of an attention block)
+    become one with the weights side by side, and slices of its result:
+        qmm(x, W1), qmm(x, W2), ...   =>   y = qmm(x, [W1 | W2 | ...]);  y[..., 0:n1], y[..., n1:n1+n2], ...
+    One launch and one pass over x instead of several; per-column scales make the concatenation exact.  The
+    reference has this rewrite for float16 matmuls only (python/hidet/graph/transforms/graph_patterns/matmul_patterns.py).
+    Runs after the epilogue fusion, which takes the gate / up pairs and the linears with a residual."""
+
+    def __init__(self):
+        super().__init__('quantized_linear_concat')
+
+    def apply(self, gm: fx.GraphModule, constants: Dict[str, torch.Tensor]) -> int:
+        buffers = dict(gm.named_buffers())
+
+        def const_of(node):
+            return buffers.get(node.target) if isinstance(node, fx.Node) and node.op == 'get_attr' else None
+
+        groups: Dict[fx.Node, List[fx.Node]] = {}
+        for node in gm.graph.nodes:
+            if QuantizedLinearEpilogueFusion._plain_qmm(node) and isinstance(node.args[0], fx.Node):
+                wq, scale = const_of(node.args[1]), const_of(node.args[2])
+                if wq is not None and scale is not None and wq.dim() == 2 and wq.dtype == torch.int8:
+                    groups.setdefault(node.args[0], []).append(node)
+        existing = sum(1 for name in buffers if name.startswith('_b200q_cat_wq_'))
+        count = 0
+        for x, members in groups.items():
+            if len(members) < 2:
+                continue
+            weights = [const_of(n.args[1]) for n in members]
+            scales = [const_of(n.args[2]) for n in members]
+            k = weights[0].shape[0]
+            if any(w.shape[0] != k or w.shape[1] % 8 for w in weights) or any(sc.dtype != scales[0].dtype for sc in scales):
+                continue
+            if not _fusable(k, sum(w.shape[1] for w in weights)):
+                continue
+            wq_name, scale_name = '_b200q_cat_wq_{}'.format(existing + count), '_b200q_cat_scale_{}'.format(existing + count)
+            gm.register_buffer(wq_name, torch.cat(weights, dim=1).contiguous())
+            gm.register_buffer(scale_name, torch.cat(scales, dim=0).contiguous())
+            with gm.graph.inserting_before(members[0]):   # every member depends on x and constants only
+                merged = gm.graph.call_function(quantized_matmul, (x, gm.graph.get_attr(wq_name), gm.graph.get_attr(scale_name)))
+                begin = 0
+                for member, w in zip(members, weights):
+                    piece = gm.graph.call_function(operator.getitem, (merged, (Ellipsis, slice(begin, begin + w.shape[1]))))
+                    member.replace_all_uses_with(piece)
+                    begin += w.shape[1]
+            for member in members:
+                gm.graph.erase_node(member)
+            count += 1
+        if count:
+            drop_unused_constants(gm)
+            used = {n.target for n in gm.graph.nodes if n.op == 'get_attr'}
+            for name in list(buffers):
+                if name.startswith('_b200q_') and name not in used and hasattr(gm, name):
+                    delattr(gm, name)
+        return count
+
+
 def quantized_embedding(indices: torch.Tensor, wq: torch.Tensor, scale: torch.Tensor) -> torch.Tensor:
     """The call the rewritten graph makes for an embedding: lookup in the row-quantized table."""
     return quant.symmetric_dequantize_take(wq, scale, indices)
@@ -412,6 +469,7 @@ def symmetric_embedding_quantize_patterns(quant_type: str = 'int8') -> List[Subg
 
 def default_patterns() -> List[SubgraphRewriteRule]:
     """python/hidet/graph/transforms/graph_patterns/quant/__init__.py:19-28: embedding tables and linear layers; then
-    the fusion of what follows a quantized linear into its kernel (in the reference a later pass, fuse_operator)."""
+    the fusion of what follows a quantized linear into its kernel (in the reference a later pass, fuse_operator), then
+    the merging of the quantized linears that are left sharing an input."""
     return (symmetric_embedding_quantize_patterns(quant_type='int8') + symmetric_linear_patterns(quant_type='int8', dims=0) +
-            [QuantizedLinearEpilogueFusion()])
+            [QuantizedLinearEpilogueFusion(), QuantizedLinearConcat()])

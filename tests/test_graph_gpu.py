@@ -223,11 +223,12 @@ def test_epilogue_fusion_folds_swiglu_and_residuals_into_the_kernels():
         hg.optimize(gm)
     calls = [n for n in gm.graph.nodes if n.op == 'call_function' and n.target is hg.quantized_matmul]
     kinds = sorted((tuple(sorted(n.kwargs)) for n in calls))
-    # q, k, v plain; o and down with the residual; gate and up as one launch with the SwiGLU pairing
-    assert kinds == [(), (), (), ('activation',), ('residual',), ('residual',)]
+    # q, k, v as one plain launch; o and down with the residual; gate and up as one launch with the SwiGLU pairing
+    assert kinds == [(), ('activation',), ('residual',), ('residual',)]
     buffers = dict(gm.named_buffers())
     assert tuple(buffers['_b200q_gu_wq_0'].shape) == (256, 2 * 688)
-    assert sum(1 for name in buffers if name.startswith('_b200q_wq_')) == 5   # the separate gate and up weights are gone
+    assert tuple(buffers['_b200q_cat_wq_0'].shape) == (256, 3 * 256)
+    assert sum(1 for name in buffers if name.startswith('_b200q_wq_')) == 2   # o and down; the separate q, k, v, gate and up weights are gone
     with torch.no_grad():
         got = gm(x)
     assert (got.float() - want.float()).abs().max() < 5e-2
@@ -290,3 +291,42 @@ def test_compiled_graph_is_not_reused_with_another_module_s_weights():
         second.weight.mul_(0.5)
         second.weight[3, :] = 1.0
         assert torch.equal(compiled_second(x), reference(second, x))
+
+
+def test_linears_of_one_input_are_merged_into_one_launch():
+    """Query, key and value projections share their input: after the pass there is one quantized linear with the three
+    weights side by side, and slices of its result stand where the three results stood."""
+    class Attn(nn.Module):
+        def __init__(self):
+            super().__init__()
+            self.q = nn.Linear(256, 256, bias=False)
+            self.k = nn.Linear(256, 128, bias=False)
+            self.v = nn.Linear(256, 128, bias=False)
+            self.o = nn.Linear(256, 256, bias=False)
+
+        def forward(self, x):
+            q, k, v = self.q(x), self.k(x), self.v(x)
+            return x + self.o(q * torch.cat((k, v), dim=-1))
+
+    torch.manual_seed(5)
+    model = Attn().half().cuda().eval()
+    x = torch.randn(2, 7, 256, device='cuda').half()
+    gm = fx.symbolic_trace(model)
+    with torch.no_grad(), hg.PassContext() as ctx:
+        ctx.set_precision('int8')
+        hg.optimize(gm)
+        got = gm(x)
+
+        def qlin(lin, inp, **kw):
+            wq, scale = hidet_b200.symmetric_quantize(lin.weight.detach().t().contiguous(), 'int8', dims=0)
+            return hidet_b200.symmetric_quant_matmul(inp, wq, scale, **kw)
+
+        q, k, v = qlin(model.q, x), qlin(model.k, x), qlin(model.v, x)
+        want = qlin(model.o, q * torch.cat((k, v), dim=-1), residual=x)
+    calls = [n for n in gm.graph.nodes if n.op == 'call_function' and n.target is hg.quantized_matmul]
+    assert len(calls) == 2                                   # q | k | v in one, o (with the residual folded in)
+    merged = calls[0]
+    assert dict(gm.named_buffers())[merged.args[1].target].shape == (256, 512)
+    # the merged launch may cut K elsewhere than the three separate ones: the last bit of a partial sum can differ
+    assert (got.float() - want.float()).abs().max() <= 2e-3 * want.float().abs().max()
+    assert torch.equal(got, gm(x))

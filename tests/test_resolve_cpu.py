@@ -32,9 +32,9 @@ def test_pass_context_precision_switch():
         assert ctx.configs['quantize_patterns'] == []
         ctx.set_precision('int8')
         assert ctx.configs['precision'] == 'float16'     # as in the reference (base.py:136-141)
-        assert len(ctx.configs['quantize_patterns']) == len(default_patterns()) == 5  # embedding, constant right, constant left, two-step fusion, epilogue fusion
+        assert len(ctx.configs['quantize_patterns']) == len(default_patterns()) == 6  # embedding, constant right, constant left, two-step fusion, epilogue fusion, concatenation
         ctx.add_quantize_rules([SymmetricLinearQuantizePattern])
-        assert len(ctx.configs['quantize_patterns']) == 6
+        assert len(ctx.configs['quantize_patterns']) == 7
         assert PassContext.current() is ctx
     with pytest.raises(ValueError):
         SymmetricLinearQuantizePattern(quant_type='int16')
