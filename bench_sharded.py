@@ -236,7 +236,8 @@ def run_sharded(args) -> int:
 
     if rank == 0:
         uses_multicast = args.gather == 'p2p' and any(po.multicast_ptrs and po.multicast_ptrs[0] for layer in layers for po in layer._peer_outputs.values())
-        large_m_delivery = ('one multimem.st per 16 bytes to the NVLink multicast mapping of the outputs' if uses_multicast and multicast
+        large_m_delivery = ('one multimem.st per 16 bytes to the NVLink multicast mapping of the outputs'
+                            if uses_multicast and multicast and world >= ColumnParallelQuantLinear.MULTICAST_MIN_WORLD
                             else 'peer stores to every rank' if args.gather == 'p2p' else 'NCCL all-gather')
         line = {
             'metric': 'quant-linear HBM GB/s (70B-shaped layer, column-parallel)', 'value': value, 'unit': 'GB/s', 'n_gpus': world,

@@ -122,6 +122,7 @@ class ColumnParallelQuantLinear:
     """
 
     MULTICAST_MIN_ROWS = 33   # what the large-M kernel serves
+    MULTICAST_MIN_WORLD = 4   # with one peer a multicast store only adds this GPU's own copy to the link traffic (measured: slower)
 
     def __init__(self, wq_shard: torch.Tensor, scale_shard: torch.Tensor, group=None, gather: str = 'nccl', multicast: bool = True):
         if wq_shard.dtype != torch.int8 or wq_shard.dim() != 2:
@@ -195,7 +196,7 @@ class ColumnParallelQuantLinear:
             ws_bytes = ffi.func('b200q_qlinear_workspace_bytes')(rows, n_local, k, ffi.LAYOUT_KN)
             ws_ptr, ws_size = workspaces.get(x.device, ws_bytes)
             main = torch.cuda.current_stream(x.device)
-            if multicast_ptr and self.multicast and rows >= self.MULTICAST_MIN_ROWS:
+            if multicast_ptr and self.multicast and rows >= self.MULTICAST_MIN_ROWS and self.world >= self.MULTICAST_MIN_WORLD:
                 # large M: every 16 bytes leave this GPU once and the switch delivers them to all ranks
                 ffi.func('b200q_qlinear_f16_i8_to_multicast')(x.data_ptr(), self.wq.data_ptr(), self.scale.data_ptr(), multicast_ptr, n, c0,
                                                             rows, n_local, k, ws_ptr, ws_size, main.cuda_stream)
