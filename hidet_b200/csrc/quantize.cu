@@ -144,6 +144,52 @@ __device__ __forceinline__ void store_vec(T *p, const Vec<T, N> &x) {
     *reinterpret_cast<Vec<T, N> *>(p) = x;
 }
 
+// VEC quotients -> codes.  The general form applies Arith<T>::quant element by element.
+template <typename T, typename Q, int VEC, typename D>
+struct QuantVec {
+    // scales: one divisor per element (PER_ELEMENT) or one for all
+    template <bool PER_ELEMENT>
+    static __device__ __forceinline__ void run(const Vec<T, VEC> &x, const D *s, Vec<Q, VEC> &q) {
+#pragma unroll
+        for (int i = 0; i < VEC; ++i) q.v[i] = Arith<T>::template quant<Q>(x.v[i], s[PER_ELEMENT ? i : 0]);
+    }
+};
+
+// f16 -> int8, eight at a time, two per instruction where the arithmetic allows it, with the same bits as the
+// general form:
+//   * the quotient is f16(rcp * f32(w)) as in Arith<__half>::div_prepared; the correction step there only touches
+//     non-zero quotients below 0x008F (8.5e-6), which round to zero either way, so it is left out;
+//   * hrint on both halves at once; the rounded value r is an integer, and for |r| <= 127 the f16 sum r + 1536 is
+//     exact and carries r's two's-complement byte in its low mantissa bits (1536 = 0x6600, ulp 1), which replaces the
+//     two conversions (short)(r), (int8_t)(short);
+//   * a pair with a rounded value that is not a number of magnitude <= 127 (a zero scale gives 0 * inf = NaN, or
+//     inf) takes the general form, whose conversions define what those become.
+template <>
+struct QuantVec<__half, int8_t, 8, Arith<__half>::Divisor> {
+    template <bool PER_ELEMENT>
+    static __device__ __forceinline__ void run(const Vec<__half, 8> &x, const Arith<__half>::Divisor *s, Vec<int8_t, 8> &q) {
+        const __half2 *x2 = reinterpret_cast<const __half2 *>(x.v);
+        uint32_t biased[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const Arith<__half>::Divisor &d0 = s[PER_ELEMENT ? 2 * j : 0], &d1 = s[PER_ELEMENT ? 2 * j + 1 : 0];
+            const float2 f = __half22float2(x2[j]);
+            const __half2 r = h2rint(__floats2half2_rn(d0.rcp * f.x, d1.rcp * f.y));
+            const __half2 in_range = __hle2(__habs2(r), __floats2half2_rn(127.0f, 127.0f));  // 1.0 where true; false for NaN
+            __half2 b = __hadd2(r, __floats2half2_rn(1536.0f, 1536.0f));
+            uint32_t bits = *reinterpret_cast<const uint32_t *>(&b);
+            if (*reinterpret_cast<const uint32_t *>(&in_range) != 0x3C003C00u) {
+                const uint32_t lo = (uint8_t)Arith<__half>::quant<int8_t>(x.v[2 * j], d0), hi = (uint8_t)Arith<__half>::quant<int8_t>(x.v[2 * j + 1], d1);
+                bits = lo | (hi << 16);
+            }
+            biased[j] = bits;
+        }
+        uint32_t *out = reinterpret_cast<uint32_t *>(q.v);
+        out[0] = __byte_perm(biased[0], biased[1], 0x6420);  // the low byte of each half, in order
+        out[1] = __byte_perm(biased[2], biased[3], 0x6420);
+    }
+};
+
 constexpr int kThreads = 256;
 
 // ---------------------------------------------------------------------------------------------
@@ -230,8 +276,7 @@ __global__ void __launch_bounds__(kThreads) quantize_cols_kernel(const T *__rest
         for (int64_t r = ty; r < nrows; r += TY) {
             Vec<T, VEC> x = cache ? load_vec<T, VEC>(tile + r * PW + tx * VEC) : load_vec<T, VEC>(src + r * cols);
             Vec<Q, VEC> q;
-#pragma unroll
-            for (int i = 0; i < VEC; ++i) q.v[i] = A::template quant<Q>(x.v[i], s[i]);
+            QuantVec<T, Q, VEC, typename A::Divisor>::template run<true>(x, s, q);
             store_vec<Q, VEC>(dst + r * cols, q);
         }
     }
@@ -298,16 +343,14 @@ __global__ void __launch_bounds__(kThreads) quantize_rows_kernel(const T *__rest
         const int64_t i = threadIdx.x + j * stride;
         if (i < nvec) {
             Vec<Q, VEC> q;
-#pragma unroll
-            for (int e = 0; e < VEC; ++e) q.v[e] = A::template quant<Q>(keep[j].v[e], s);
+            QuantVec<T, Q, VEC, typename A::Divisor>::template run<false>(keep[j], &s, q);
             store_vec<Q, VEC>(dst + i * VEC, q);
         }
     }
     for (int64_t i = threadIdx.x + REG_CHUNKS * stride; i < nvec; i += stride) {
         Vec<T, VEC> x = load_vec<T, VEC>(src + i * VEC);
         Vec<Q, VEC> q;
-#pragma unroll
-        for (int e = 0; e < VEC; ++e) q.v[e] = A::template quant<Q>(x.v[e], s);
+        QuantVec<T, Q, VEC, typename A::Divisor>::template run<false>(x, &s, q);
         store_vec<Q, VEC>(dst + i * VEC, q);
     }
 }
