@@ -157,26 +157,28 @@ struct QuantVec {
 
 // f16 -> int8, eight at a time, two per instruction where the arithmetic allows it, with the same bits as the
 // general form:
-//   * the quotient is f16(rcp * f32(w)) as in Arith<__half>::div_prepared; the correction step there only touches
+//   * the quotient v is f16(rcp * f32(w)) as in Arith<__half>::div_prepared; the correction step there only touches
 //     non-zero quotients below 0x008F (8.5e-6), which round to zero either way, so it is left out;
-//   * hrint on both halves at once; the rounded value r is an integer, and for |r| <= 127 the f16 sum r + 1536 is
-//     exact and carries r's two's-complement byte in its low mantissa bits (1536 = 0x6600, ulp 1), which replaces the
-//     two conversions (short)(r), (int8_t)(short);
-//   * a pair with a rounded value that is not a number of magnitude <= 127 (a zero scale gives 0 * inf = NaN, or
-//     inf) takes the general form, whose conversions define what those become.
+//   * b = v + 1536 in f16 (1536 = 0x6600, where one ulp is 1) is v rounded to an integer, ties to even, plus 1536
+//     for |v| < 512: the same integer hrint gives, and 1536 being even the same ties.  For |hrint(v)| <= 127 the
+//     low mantissa byte of b is that integer's two's-complement byte, which replaces hrint and the two conversions
+//     (short)(r), (int8_t)(short);
+//   * b - 1536 is exact; where its magnitude is not a number <= 127 (|v| >= 512 lands there too, and so do the NaN
+//     and infinities a zero scale produces) the pair takes the general form, whose conversions define the result.
 template <>
 struct QuantVec<__half, int8_t, 8, Arith<__half>::Divisor> {
     template <bool PER_ELEMENT>
     static __device__ __forceinline__ void run(const Vec<__half, 8> &x, const Arith<__half>::Divisor *s, Vec<int8_t, 8> &q) {
         const __half2 *x2 = reinterpret_cast<const __half2 *>(x.v);
+        const __half2 magic = __floats2half2_rn(1536.0f, 1536.0f);
+        const __half2 limit = __floats2half2_rn(127.0f, 127.0f);
         uint32_t biased[4];
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
             const Arith<__half>::Divisor &d0 = s[PER_ELEMENT ? 2 * j : 0], &d1 = s[PER_ELEMENT ? 2 * j + 1 : 0];
             const float2 f = __half22float2(x2[j]);
-            const __half2 r = h2rint(__floats2half2_rn(d0.rcp * f.x, d1.rcp * f.y));
-            const __half2 in_range = __hle2(__habs2(r), __floats2half2_rn(127.0f, 127.0f));  // 1.0 where true; false for NaN
-            __half2 b = __hadd2(r, __floats2half2_rn(1536.0f, 1536.0f));
+            const __half2 b = __hadd2(__floats2half2_rn(d0.rcp * f.x, d1.rcp * f.y), magic);
+            const __half2 in_range = __hle2(__habs2(__hsub2(b, magic)), limit);  // 1.0 where true; false for NaN
             uint32_t bits = *reinterpret_cast<const uint32_t *>(&b);
             if (*reinterpret_cast<const uint32_t *>(&in_range) != 0x3C003C00u) {
                 const uint32_t lo = (uint8_t)Arith<__half>::quant<int8_t>(x.v[2 * j], d0), hi = (uint8_t)Arith<__half>::quant<int8_t>(x.v[2 * j + 1], d1);
@@ -190,27 +192,91 @@ struct QuantVec<__half, int8_t, 8, Arith<__half>::Divisor> {
     }
 };
 
+// The running absmax of VEC columns, in the reference's sense: max over abs_(w), starting from lowest().
+template <typename T, int VEC>
+struct AbsMaxVec {
+    T m[VEC];
+    __device__ __forceinline__ void init() {
+#pragma unroll
+        for (int i = 0; i < VEC; ++i) m[i] = Arith<T>::lowest();
+    }
+    __device__ __forceinline__ void add(const Vec<T, VEC> &x) {
+#pragma unroll
+        for (int i = 0; i < VEC; ++i) m[i] = Arith<T>::max_(m[i], Arith<T>::abs_(x.v[i]));
+    }
+    __device__ __forceinline__ void result(T *out) const {
+#pragma unroll
+        for (int i = 0; i < VEC; ++i) out[i] = m[i];
+    }
+};
+
+// f16, two columns per instruction: the running maximum `hi` and minimum `lo` of the values themselves (__hmax2 /
+// __hmin2 skip a NaN operand and order -0 below +0, exactly as the __hmax of the element-wise form does), folded
+// at the end.  abs_ leaves w >= 0 (both zeros and +inf included) as it is, negates w < 0, and turns a NaN into a
+// NaN, which max_ skips; so the element-wise result over a set of values is
+//     max(lowest, the largest non-NaN value, -(the smallest value) if that one is below zero)
+// and hi starts at lowest.  The zero cases: only -0 (and NaN) seen gives hi = lo = -0 and the result -0, as the
+// element-wise form gives; one +0 makes hi = +0.  Nothing seen, or only NaN, leaves lowest.
+template <>
+struct AbsMaxVec<__half, 8> {
+    __half2 hi[4], lo[4];
+    __device__ __forceinline__ void init() {
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            hi[j] = __floats2half2_rn(-65504.0f, -65504.0f);
+            lo[j] = __floats2half2_rn(65504.0f, 65504.0f);
+        }
+    }
+    __device__ __forceinline__ void add(const Vec<__half, 8> &x) {
+        const __half2 *x2 = reinterpret_cast<const __half2 *>(x.v);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            hi[j] = __hmax2(hi[j], x2[j]);
+            lo[j] = __hmin2(lo[j], x2[j]);
+        }
+    }
+    __device__ __forceinline__ void result(__half *out) const {
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const __half h[2] = {__low2half(hi[j]), __high2half(hi[j])}, l[2] = {__low2half(lo[j]), __high2half(lo[j])};
+#pragma unroll
+            for (int e = 0; e < 2; ++e) out[2 * j + e] = __hlt(l[e], (__half)0.0f) ? __hmax(h[e], __hneg(l[e])) : h[e];
+        }
+    }
+};
+
 constexpr int kThreads = 256;
 
 // ---------------------------------------------------------------------------------------------
 // reduce over rows (Hidet dims=0): scale[cols]
 // ---------------------------------------------------------------------------------------------
-// grid = (cluster_size, panels); the CTAs of one cluster share blockIdx.y (a panel of TX*VEC
-// columns) and split the rows.  cache != 0: the CTA's rows of the panel are kept in dynamic shared
-// memory between the two phases; cache == 0: phase 2 reads them again from global memory.
-template <typename T, typename Q, int VEC>
+// 16 bytes global -> shared without passing through registers.
+__device__ __forceinline__ void copy_async_16(uint32_t dst, const void *src) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src) : "memory");
+}
+// All of this thread's earlier asynchronous copies have landed.
+__device__ __forceinline__ void copy_async_wait_all() { asm volatile("cp.async.wait_all;" ::: "memory"); }
+
+// grid = (cluster_size, panels); the CTAs of one cluster share blockIdx.y (a panel of PW = TX*VEC
+// columns) and split the rows.  TX threads lie across a panel row, kThreads / TX rows make a sweep.
+// cache != 0: the CTA's rows of the panel are kept in dynamic shared memory between the two phases
+// (with VEC > 1 they are brought there by asynchronous 16-byte copies, all in flight at once, and the
+// absmax is taken from shared memory); cache == 0: phase 2 reads them again from global memory.
+// Each thread reads back only what it copied itself, so the copies need no barrier.
+template <typename T, typename Q, int VEC, int TX>
 __global__ void __launch_bounds__(kThreads) quantize_cols_kernel(const T *__restrict__ w, Q *__restrict__ wq,
                                                                  T *__restrict__ scale, int64_t rows, int64_t cols,
                                                                  int64_t rows_per_cta, int cache) {
-    constexpr int TX = (VEC == 1) ? 32 : 8;    // threads across a panel row
     constexpr int TY = kThreads / TX;          // rows per sweep
     constexpr int PW = TX * VEC;               // panel width in elements
+    constexpr int WARPS = kThreads / 32;
+    constexpr bool ASYNC = VEC > 1;            // a vector is 16 bytes whenever VEC > 1
     using A = Arith<T>;
 
     extern __shared__ __align__(16) unsigned char smem_raw[];
-    __shared__ T red[TY][PW];
+    __shared__ __align__(16) T red[WARPS][PW];
     __shared__ T part[PW];
-    __shared__ T amax_s[PW];
+    __shared__ __align__(16) typename A::Divisor div_s[PW];
 
     T *tile = reinterpret_cast<T *>(smem_raw);
 
@@ -220,34 +286,54 @@ __global__ void __launch_bounds__(kThreads) quantize_cols_kernel(const T *__rest
     const int64_t col = (int64_t)blockIdx.y * PW + (int64_t)tx * VEC;
     const bool col_ok = col < cols;            // cols % VEC == 0 whenever VEC > 1
     const int64_t row0 = (int64_t)blockIdx.x * rows_per_cta;
-    int64_t nrows = rows - row0;
-    if (nrows > rows_per_cta) nrows = rows_per_cta;
-    if (nrows < 0) nrows = 0;
+    int64_t nrows64 = rows - row0;
+    if (nrows64 > rows_per_cta) nrows64 = rows_per_cta;
+    if (nrows64 < 0) nrows64 = 0;
+    const int nrows = (int)nrows64;            // at most rows_per_cta, which the launcher keeps below 2^31
+    const int64_t sweep = (int64_t)TY * cols;  // elements between two rows of this thread
 
     // ---- phase 1: partial absmax of this CTA's rows ----
-    T m[VEC];
-#pragma unroll
-    for (int i = 0; i < VEC; ++i) m[i] = A::lowest();
+    AbsMaxVec<T, VEC> acc;
+    acc.init();
     if (col_ok) {
-        const T *src = w + row0 * cols + col;
+        const T *src = w + (row0 + ty) * cols + col;
+        if (ASYNC && cache) {
+            uint32_t dst = smem_u32(tile) + (uint32_t)((ty * PW + tx * VEC) * sizeof(T));
+            for (int r = ty; r < nrows; r += TY, src += sweep, dst += (uint32_t)(TY * PW * sizeof(T))) copy_async_16(dst, src);
+            copy_async_wait_all();
+            const T *t = tile + ty * PW + tx * VEC;
 #pragma unroll 4
-        for (int64_t r = ty; r < nrows; r += TY) {
-            Vec<T, VEC> x = load_vec<T, VEC>(src + r * cols);
-            if (cache) store_vec<T, VEC>(tile + r * PW + tx * VEC, x);
-#pragma unroll
-            for (int i = 0; i < VEC; ++i) m[i] = A::max_(m[i], A::abs_(x.v[i]));
+            for (int r = ty; r < nrows; r += TY, t += TY * PW) acc.add(load_vec<T, VEC>(t));
+        } else {
+            T *t = tile + ty * PW + tx * VEC;
+#pragma unroll 4
+            for (int r = ty; r < nrows; r += TY, src += sweep, t += TY * PW) {
+                Vec<T, VEC> x = load_vec<T, VEC>(src);
+                if (cache) store_vec<T, VEC>(t, x);
+                acc.add(x);
+            }
         }
     }
+    T m[VEC];
+    acc.result(m);
+    // the rows of one sweep that a warp holds: lanes tx, tx + TX, tx + 2 TX, ...
 #pragma unroll
-    for (int i = 0; i < VEC; ++i) red[ty][tx * VEC + i] = m[i];
+    for (int off = TX; off < 32; off <<= 1) {
+#pragma unroll
+        for (int i = 0; i < VEC; ++i) m[i] = A::max_(m[i], __shfl_xor_sync(0xffffffffu, m[i], off));
+    }
+    if ((threadIdx.x & 31) < TX) {
+#pragma unroll
+        for (int i = 0; i < VEC; ++i) red[threadIdx.x >> 5][tx * VEC + i] = m[i];
+    }
     __syncthreads();
     if (threadIdx.x < PW) {
         T a = A::lowest();
 #pragma unroll
-        for (int j = 0; j < TY; ++j) a = A::max_(a, red[j][threadIdx.x]);
+        for (int j = 0; j < WARPS; ++j) a = A::max_(a, red[j][threadIdx.x]);
         part[threadIdx.x] = a;
     }
-    // ---- exchange partial maxima inside the cluster ----
+    // ---- exchange partial maxima inside the cluster; one thread per column makes its scale and divisor ----
     cluster.sync();
     if (threadIdx.x < PW) {
         T a = A::lowest();
@@ -256,28 +342,27 @@ __global__ void __launch_bounds__(kThreads) quantize_cols_kernel(const T *__rest
             const T *remote = cluster.map_shared_rank(part, r);
             a = A::max_(a, remote[threadIdx.x]);
         }
-        amax_s[threadIdx.x] = a;
-    }
-    cluster.sync();  // nobody leaves (or overwrites part) while a peer may still read it
-
-    // ---- phase 2: scale and quantize ----
-    const T qm = A::qmax(QMax<Q>::value);
-    if (blockIdx.x == 0 && threadIdx.x < PW) {
+        const T s = A::div_(a, A::qmax(QMax<Q>::value));
+        div_s[threadIdx.x] = A::prepare(s);
         const int64_t c = (int64_t)blockIdx.y * PW + threadIdx.x;
-        if (c < cols) scale[c] = A::div_(amax_s[threadIdx.x], qm);
+        if (blockIdx.x == 0 && c < cols) scale[c] = s;
     }
+    cluster.sync();  // div_s is complete, and nobody leaves while a peer may still read its part
+
+    // ---- phase 2: quantize ----
     if (col_ok) {
         typename A::Divisor s[VEC];
 #pragma unroll
-        for (int i = 0; i < VEC; ++i) s[i] = A::prepare(A::div_(amax_s[tx * VEC + i], qm));
-        const T *src = w + row0 * cols + col;
-        Q *dst = wq + row0 * cols + col;
+        for (int i = 0; i < VEC; ++i) s[i] = div_s[tx * VEC + i];
+        const T *src = w + (row0 + ty) * cols + col;
+        Q *dst = wq + (row0 + ty) * cols + col;
+        const T *t = tile + ty * PW + tx * VEC;
 #pragma unroll 4
-        for (int64_t r = ty; r < nrows; r += TY) {
-            Vec<T, VEC> x = cache ? load_vec<T, VEC>(tile + r * PW + tx * VEC) : load_vec<T, VEC>(src + r * cols);
+        for (int r = ty; r < nrows; r += TY, src += sweep, dst += sweep, t += TY * PW) {
+            Vec<T, VEC> x = cache ? load_vec<T, VEC>(t) : load_vec<T, VEC>(src);
             Vec<Q, VEC> q;
             QuantVec<T, Q, VEC, typename A::Divisor>::template run<true>(x, s, q);
-            store_vec<Q, VEC>(dst + r * cols, q);
+            store_vec<Q, VEC>(dst, q);
         }
     }
 }
@@ -309,21 +394,22 @@ __global__ void __launch_bounds__(kThreads) quantize_rows_kernel(const T *__rest
     const int64_t stride = blockDim.x;
 
     Vec<T, VEC> keep[REG_CHUNKS];
-    T m = A::lowest();
+    AbsMaxVec<T, VEC> acc;
+    acc.init();
 #pragma unroll
     for (int j = 0; j < REG_CHUNKS; ++j) {
         const int64_t i = threadIdx.x + j * stride;
         if (i < nvec) {
             keep[j] = load_vec<T, VEC>(src + i * VEC);
-#pragma unroll
-            for (int e = 0; e < VEC; ++e) m = A::max_(m, A::abs_(keep[j].v[e]));
+            acc.add(keep[j]);
         }
     }
-    for (int64_t i = threadIdx.x + REG_CHUNKS * stride; i < nvec; i += stride) {
-        Vec<T, VEC> x = load_vec<T, VEC>(src + i * VEC);
+    for (int64_t i = threadIdx.x + REG_CHUNKS * stride; i < nvec; i += stride) acc.add(load_vec<T, VEC>(src + i * VEC));
+    T each[VEC];
+    acc.result(each);
+    T m = A::lowest();
 #pragma unroll
-        for (int e = 0; e < VEC; ++e) m = A::max_(m, A::abs_(x.v[e]));
-    }
+    for (int e = 0; e < VEC; ++e) m = A::max_(m, each[e]);
     m = warp_max<T>(m);
     if ((threadIdx.x & 31) == 0) warp_part[threadIdx.x >> 5] = m;
     __syncthreads();
@@ -356,30 +442,75 @@ __global__ void __launch_bounds__(kThreads) quantize_rows_kernel(const T *__rest
 }
 
 // ---------------------------------------------------------------------------------------------
-// dequantize: one vector of VEC quantized values per thread
+// dequantize: a CTA covers kDqRows rows of kDqVecs vectors; a thread keeps its column and walks the rows
 // ---------------------------------------------------------------------------------------------
+// VEC codes -> values.  The general form applies Arith<T>::dequant element by element.
+template <typename T, typename Q, int VEC>
+struct DequantVec {
+    template <bool PER_ELEMENT>
+    static __device__ __forceinline__ void run(const Vec<Q, VEC> &q, const T *s, Vec<T, VEC> &out) {
+#pragma unroll
+        for (int e = 0; e < VEC; ++e) out.v[e] = Arith<T>::template dequant<Q>(q.v[e], s[PER_ELEMENT ? e : 0]);
+    }
+};
+
+// int8 -> f16, two per instruction with the same bits: 0x6400 | (b ^ 0x80) is the f16 number 1024 + (b + 128), and
+// subtracting 1152 leaves b exactly, the value __short2half_rn gives; the product with the scale is then the same
+// single f16 multiplication.
+template <>
+struct DequantVec<__half, int8_t, 8> {
+    template <bool PER_ELEMENT>
+    static __device__ __forceinline__ void run(const Vec<int8_t, 8> &q, const __half *s, Vec<__half, 8> &out) {
+        const uint32_t *qw = reinterpret_cast<const uint32_t *>(q.v);
+        const __half2 *s2 = reinterpret_cast<const __half2 *>(s);
+        const __half2 s_all = PER_ELEMENT ? __half2() : __half2half2(s[0]);
+        __half2 *o2 = reinterpret_cast<__half2 *>(out.v);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            // bytes (2j, 2j+1) of the vector into the low bytes of the two halves, 0x64 above each, sign bit flipped
+            const uint32_t placed = __byte_perm(qw[j >> 1], 0x64646464u, (j & 1) ? 0x4342 : 0x4140) ^ 0x00800080u;
+            uint32_t exact;
+            asm("sub.f16x2 %0, %1, %2;" : "=r"(exact) : "r"(placed), "r"(0x64806480u));
+            o2[j] = __hmul2(*reinterpret_cast<const __half2 *>(&exact), PER_ELEMENT ? s2[j] : s_all);
+        }
+    }
+};
+
+constexpr int kDqVecs = 32;                       // vectors across a CTA (one warp wide)
+constexpr int kDqSweep = kThreads / kDqVecs;      // rows per sweep
+constexpr int kDqRows = 4 * kDqSweep;             // rows per CTA
+
+// grid = (row blocks, column blocks)
 template <typename T, typename Q, int VEC>
 __global__ void __launch_bounds__(kThreads) dequantize_kernel(const Q *__restrict__ wq, const T *__restrict__ scale,
                                                               T *__restrict__ w, int64_t rows, int64_t cols,
                                                               int reduce_dim) {
-    using A = Arith<T>;
-    const int64_t vec_per_row = cols / VEC;
-    const int64_t total = rows * vec_per_row;
-    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
-        const int64_t r = i / vec_per_row;
-        const int64_t c = (i - r * vec_per_row) * VEC;
-        Vec<Q, VEC> q = load_vec<Q, VEC>(wq + r * cols + c);
-        Vec<T, VEC> out;
-        if (reduce_dim == 0) {
-            Vec<T, VEC> s = load_vec<T, VEC>(scale + c);
+    const int64_t c = ((int64_t)blockIdx.y * kDqVecs + (threadIdx.x % kDqVecs)) * VEC;
+    if (c >= cols) return;                        // cols % VEC == 0 whenever VEC > 1
+    const int64_t r0 = (int64_t)blockIdx.x * kDqRows + threadIdx.x / kDqVecs;
+    const Q *src = wq + r0 * cols + c;
+    T *dst = w + r0 * cols + c;
+    const int64_t sweep = (int64_t)kDqSweep * cols;
+    if (reduce_dim == 0) {
+        const Vec<T, VEC> s = load_vec<T, VEC>(scale + c);
 #pragma unroll
-            for (int e = 0; e < VEC; ++e) out.v[e] = A::template dequant<Q>(q.v[e], s.v[e]);
-        } else {
-            const T s = scale[r];
-#pragma unroll
-            for (int e = 0; e < VEC; ++e) out.v[e] = A::template dequant<Q>(q.v[e], s);
+        for (int i = 0; i < kDqRows / kDqSweep; ++i) {
+            if (r0 + i * kDqSweep < rows) {
+                Vec<T, VEC> out;
+                DequantVec<T, Q, VEC>::template run<true>(load_vec<Q, VEC>(src + i * sweep), s.v, out);
+                store_vec<T, VEC>(dst + i * sweep, out);
+            }
         }
-        store_vec<T, VEC>(w + r * cols + c, out);
+    } else {
+#pragma unroll
+        for (int i = 0; i < kDqRows / kDqSweep; ++i) {
+            if (r0 + i * kDqSweep < rows) {
+                const T s = scale[r0 + i * kDqSweep];
+                Vec<T, VEC> out;
+                DequantVec<T, Q, VEC>::template run<false>(load_vec<Q, VEC>(src + i * sweep), &s, out);
+                store_vec<T, VEC>(dst + i * sweep, out);
+            }
+        }
     }
 }
 
@@ -422,9 +553,12 @@ __global__ void __launch_bounds__(kThreads) embedding_dequant_kernel(const Q *__
 // Largest dynamic shared memory a quantize_cols CTA may ask for (the static arrays need a little).
 constexpr size_t kMaxTileBytes = 200 * 1024;
 
-template <typename T, typename Q, int VEC>
+// Threads across a panel row when a thread moves a 16-byte vector: 4 make a panel of 64 bytes per row (32 f16
+// columns), so that a [4096, 4096] weight gives 1024 CTAs of 32 KB, several to an SM and more than one wave.
+constexpr int kPanelThreads = 4;
+
+template <typename T, typename Q, int VEC, int TX>
 int launch_quantize_cols(const T *w, Q *wq, T *scale, int64_t rows, int64_t cols, cudaStream_t stream) {
-    constexpr int TX = (VEC == 1) ? 32 : 8;
     constexpr int TY = kThreads / TX;
     constexpr int PW = TX * VEC;
     const int64_t panels = ceil_div(cols, PW);
@@ -441,7 +575,7 @@ int launch_quantize_cols(const T *w, Q *wq, T *scale, int64_t rows, int64_t cols
         cache = 0;
         tile_bytes = 0;
     }
-    auto kernel = quantize_cols_kernel<T, Q, VEC>;
+    auto kernel = quantize_cols_kernel<T, Q, VEC, TX>;
     if (tile_bytes > 48 * 1024) {
         B200Q_CUDA_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kMaxTileBytes));
     }
@@ -480,8 +614,8 @@ int quantize_typed(const void *w_, void *wq_, void *scale_, int64_t rows, int64_
     constexpr int VEC = 16 / sizeof(T);
     const bool vec_ok = (cols % VEC == 0) && aligned(w, 16) && aligned(wq, VEC * sizeof(Q));
     if (reduce_dim == 0) {
-        return vec_ok ? launch_quantize_cols<T, Q, VEC>(w, wq, scale, rows, cols, stream)
-                      : launch_quantize_cols<T, Q, 1>(w, wq, scale, rows, cols, stream);
+        return vec_ok ? launch_quantize_cols<T, Q, VEC, kPanelThreads>(w, wq, scale, rows, cols, stream)
+                      : launch_quantize_cols<T, Q, 1, 32>(w, wq, scale, rows, cols, stream);
     }
     return vec_ok ? launch_quantize_rows<T, Q, VEC>(w, wq, scale, rows, cols, stream)
                   : launch_quantize_rows<T, Q, 1>(w, wq, scale, rows, cols, stream);
@@ -495,15 +629,17 @@ int dequantize_typed(const void *wq_, const void *scale_, void *w_, int64_t rows
     T *w = static_cast<T *>(w_);
     constexpr int VEC = 16 / sizeof(T);  // 16-byte scale / output vectors; input vector is VEC * sizeof(Q)
     const bool vec_ok = (cols % VEC == 0) && aligned(w, 16) && aligned(wq, VEC * sizeof(Q)) && aligned(scale, 16);
-    const int64_t total = rows * (vec_ok ? cols / VEC : cols);
-    int64_t blocks = ceil_div(total, kThreads);
-    const int64_t cap = (int64_t)sm_count() * 16;
-    if (cap > 0 && blocks > cap) blocks = cap;
-    if (blocks < 1) blocks = 1;
+    if (rows == 0 || cols == 0) return B200Q_OK;
+    const int64_t row_blocks = ceil_div(rows, kDqRows);
+    const int64_t col_blocks = ceil_div(vec_ok ? cols / VEC : cols, kDqVecs);
+    if (row_blocks > 2147483647LL || col_blocks > 65535) {
+        return set_error(B200Q_UNSUPPORTED, "symmetric_dequantize: [%lld, %lld] exceeds the grid limit", (long long)rows, (long long)cols);
+    }
+    const dim3 grid((unsigned)row_blocks, (unsigned)col_blocks, 1);
     if (vec_ok) {
-        dequantize_kernel<T, Q, VEC><<<(unsigned)blocks, kThreads, 0, stream>>>(wq, scale, w, rows, cols, reduce_dim);
+        dequantize_kernel<T, Q, VEC><<<grid, kThreads, 0, stream>>>(wq, scale, w, rows, cols, reduce_dim);
     } else {
-        dequantize_kernel<T, Q, 1><<<(unsigned)blocks, kThreads, 0, stream>>>(wq, scale, w, rows, cols, reduce_dim);
+        dequantize_kernel<T, Q, 1><<<grid, kThreads, 0, stream>>>(wq, scale, w, rows, cols, reduce_dim);
     }
     B200Q_CHECK_LAUNCH("dequantize_kernel");
     return B200Q_OK;

@@ -68,6 +68,40 @@ def test_quantize_edge_values():
         _assert_same(w, 'int16', dims, 'edge values dims={} int16'.format(dims))
 
 
+def special_value_weight(rows):
+    """[rows, 64] f16 whose first columns hold NaN, infinities and signed zeros in the mixes that decide the
+    absmax: abs is `(0 <= w) ? w : -w` and max is __hmax, so a NaN is skipped, -0 stays -0 and loses to +0."""
+    rng = np.random.default_rng(14)
+    w = (rng.standard_normal((rows, 64)) * 0.02).astype(np.float16)
+    nan, inf = np.float16(np.nan), np.float16(np.inf)
+    w[:, 0] = nan                                   # nothing but NaN: the absmax stays at the lowest finite value
+    w[:, 1] = np.float16(-0.0); w[7, 1] = nan       # -0 and a NaN: absmax -0
+    w[:, 2] = np.float16(-0.0); w[rows - 1, 2] = np.float16(0.0)   # one +0 among -0: absmax +0
+    w[5, 3] = nan; w[rows // 2, 3] = -nan           # NaN of both signs inside ordinary values
+    w[3, 4] = inf                                   # +inf owns the scale
+    w[rows - 2, 5] = -inf                           # -inf does
+    w[:, 6] = -np.abs(w[:, 6]) - np.float16(1e-3)   # negative values only
+    w[:, 7] = np.float16(-65504.0)                  # the lowest finite value itself
+    w[:, 8] = np.float16(-0.0)                      # -0 only
+    w[:, 9] = np.float16(-0.0); w[1, 9] = np.float16(-6e-8)   # -0 and the negative subnormal next to it
+    return w
+
+
+@pytest.mark.parametrize('rows', [128, 1100])
+def test_quantize_nan_inf_and_signed_zero_columns(rows):
+    w = special_value_weight(rows)
+    # an odd column count takes the element-wise kernels, a multiple of eight the packed ones: the same columns
+    # must come out the same
+    wq_v, scale_v = _gpu_quantize(w, 'int8', 0)
+    wq_e, scale_e = _gpu_quantize(np.ascontiguousarray(w[:, :63]), 'int8', 0)
+    assert np.array_equal(scale_v[:63].view(np.uint16), scale_e.view(np.uint16)) and np.array_equal(wq_v[:, :63], wq_e)
+    for dims in (0, -1):
+        _assert_same(w, 'int8', dims, 'special values rows={} dims={}'.format(rows, dims))
+        _assert_same(w, 'int16', dims, 'special values rows={} dims={} int16'.format(rows, dims))
+    wt = np.ascontiguousarray(w.T)          # the same columns as rows of the row-wise form
+    _assert_same(wt, 'int8', -1, 'special values transposed rows={}'.format(rows))
+
+
 def test_quantize_tie_heavy_grid():
     # values on a coarse grid make w / scale land exactly on .5 in many places
     rng = np.random.default_rng(12)
