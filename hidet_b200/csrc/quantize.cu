@@ -16,8 +16,8 @@
 //
 // What differs from the reference is the schedule: the reference reads the weight twice from HBM
 // with one thread per column walking K serially; here a thread-block cluster owns a panel of
-// columns, each CTA keeps its slice of the panel in shared memory, partial maxima are exchanged
-// through distributed shared memory, and the slice is quantized from shared memory, so the weight
+// columns, each CTA keeps its slice of the panel in shared memory, partial maxima are written into
+// the other CTAs' shared memory, and the slice is quantized from shared memory, so the weight
 // crosses HBM once.  max is exact and order-independent, so the result does not depend on the
 // schedule.
 #include <cooperative_groups.h>
@@ -150,8 +150,12 @@ struct QuantVec {
     // scales: one divisor per element (PER_ELEMENT) or one for all
     template <bool PER_ELEMENT>
     static __device__ __forceinline__ void run(const Vec<T, VEC> &x, const D *s, Vec<Q, VEC> &q) {
+        run_n<PER_ELEMENT, VEC>(x.v, s, q.v);
+    }
+    template <bool PER_ELEMENT, int N>
+    static __device__ __forceinline__ void run_n(const T *x, const D *s, Q *q) {
 #pragma unroll
-        for (int i = 0; i < VEC; ++i) q.v[i] = Arith<T>::template quant<Q>(x.v[i], s[PER_ELEMENT ? i : 0]);
+        for (int i = 0; i < N; ++i) q[i] = Arith<T>::template quant<Q>(x[i], s[PER_ELEMENT ? i : 0]);
     }
 };
 
@@ -163,32 +167,34 @@ struct QuantVec {
 //     for |v| < 512: the same integer hrint gives, and 1536 being even the same ties.  For |hrint(v)| <= 127 the
 //     low mantissa byte of b is that integer's two's-complement byte, which replaces hrint and the two conversions
 //     (short)(r), (int8_t)(short);
-//   * b - 1536 is exact; where its magnitude is not a number <= 127 (|v| >= 512 lands there too, and so do the NaN
-//     and infinities a zero scale produces) the pair takes the general form, whose conversions define the result.
+//   * b - 1536 is exact; where its magnitude is not a number <= 127 for one of the eight (|v| >= 512 lands there too,
+//     and so do the NaN and infinities a zero scale produces) all eight take the general form, whose conversions
+//     define the result.
 template <>
 struct QuantVec<__half, int8_t, 8, Arith<__half>::Divisor> {
     template <bool PER_ELEMENT>
     static __device__ __forceinline__ void run(const Vec<__half, 8> &x, const Arith<__half>::Divisor *s, Vec<int8_t, 8> &q) {
         const __half2 *x2 = reinterpret_cast<const __half2 *>(x.v);
         const __half2 magic = __floats2half2_rn(1536.0f, 1536.0f);
-        const __half2 limit = __floats2half2_rn(127.0f, 127.0f);
-        uint32_t biased[4];
+        __half2 b[4], far[4];
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
             const Arith<__half>::Divisor &d0 = s[PER_ELEMENT ? 2 * j : 0], &d1 = s[PER_ELEMENT ? 2 * j + 1 : 0];
             const float2 f = __half22float2(x2[j]);
-            const __half2 b = __hadd2(__floats2half2_rn(d0.rcp * f.x, d1.rcp * f.y), magic);
-            const __half2 in_range = __hle2(__habs2(__hsub2(b, magic)), limit);  // 1.0 where true; false for NaN
-            uint32_t bits = *reinterpret_cast<const uint32_t *>(&b);
-            if (*reinterpret_cast<const uint32_t *>(&in_range) != 0x3C003C00u) {
-                const uint32_t lo = (uint8_t)Arith<__half>::quant<int8_t>(x.v[2 * j], d0), hi = (uint8_t)Arith<__half>::quant<int8_t>(x.v[2 * j + 1], d1);
-                bits = lo | (hi << 16);
-            }
-            biased[j] = bits;
+            b[j] = __hadd2(__floats2half2_rn(d0.rcp * f.x, d1.rcp * f.y), magic);
+            far[j] = __habs2(__hsub2(b[j], magic));
         }
+        // one test for the eight: the largest magnitude, a NaN if there is any
+        const __half2 worst = __hmax2_nan(__hmax2_nan(far[0], far[1]), __hmax2_nan(far[2], far[3]));
+        const __half2 in_range = __hle2(worst, __floats2half2_rn(127.0f, 127.0f));  // 1.0 where true; false for NaN
+        if (*reinterpret_cast<const uint32_t *>(&in_range) != 0x3C003C00u) {
+            QuantVec<__half, int8_t, 1, Arith<__half>::Divisor>::template run_n<PER_ELEMENT, 8>(x.v, s, q.v);
+            return;
+        }
+        const uint32_t *bits = reinterpret_cast<const uint32_t *>(b);
         uint32_t *out = reinterpret_cast<uint32_t *>(q.v);
-        out[0] = __byte_perm(biased[0], biased[1], 0x6420);  // the low byte of each half, in order
-        out[1] = __byte_perm(biased[2], biased[3], 0x6420);
+        out[0] = __byte_perm(bits[0], bits[1], 0x6420);  // the low byte of each half, in order
+        out[1] = __byte_perm(bits[2], bits[3], 0x6420);
     }
 };
 
@@ -246,6 +252,7 @@ struct AbsMaxVec<__half, 8> {
 };
 
 constexpr int kThreads = 256;
+constexpr int kMaxCluster = 8;   // the largest portable cluster
 
 // ---------------------------------------------------------------------------------------------
 // reduce over rows (Hidet dims=0): scale[cols]
@@ -256,6 +263,9 @@ __device__ __forceinline__ void copy_async_16(uint32_t dst, const void *src) {
 }
 // All of this thread's earlier asynchronous copies have landed.
 __device__ __forceinline__ void copy_async_wait_all() { asm volatile("cp.async.wait_all;" ::: "memory"); }
+// The two halves of a cluster barrier that publishes nothing: it only tells that every CTA of the cluster runs.
+__device__ __forceinline__ void cluster_arrive_relaxed() { asm volatile("barrier.cluster.arrive.relaxed.aligned;" ::: "memory"); }
+__device__ __forceinline__ void cluster_wait() { asm volatile("barrier.cluster.wait.aligned;" ::: "memory"); }
 
 // grid = (cluster_size, panels); the CTAs of one cluster share blockIdx.y (a panel of PW = TX*VEC
 // columns) and split the rows.  TX threads lie across a panel row, kThreads / TX rows make a sweep.
@@ -275,12 +285,13 @@ __global__ void __launch_bounds__(kThreads) quantize_cols_kernel(const T *__rest
 
     extern __shared__ __align__(16) unsigned char smem_raw[];
     __shared__ __align__(16) T red[WARPS][PW];
-    __shared__ T part[PW];
+    __shared__ T recv[kMaxCluster][PW];        // recv[r]: the partial maxima of the cluster's CTA r
     __shared__ __align__(16) typename A::Divisor div_s[PW];
 
     T *tile = reinterpret_cast<T *>(smem_raw);
 
     cg::cluster_group cluster = cg::this_cluster();
+    cluster_arrive_relaxed();                  // waited for before the first store into a peer's shared memory
     const int tx = threadIdx.x % TX;
     const int ty = threadIdx.x / TX;
     const int64_t col = (int64_t)blockIdx.y * PW + (int64_t)tx * VEC;
@@ -327,27 +338,31 @@ __global__ void __launch_bounds__(kThreads) quantize_cols_kernel(const T *__rest
         for (int i = 0; i < VEC; ++i) red[threadIdx.x >> 5][tx * VEC + i] = m[i];
     }
     __syncthreads();
+    // ---- exchange inside the cluster: every CTA writes its partial maxima into all the others' shared memory ----
+    cluster_wait();                            // every CTA of the cluster has started
+    const unsigned int n_cta = cluster.num_blocks();
     if (threadIdx.x < PW) {
         T a = A::lowest();
 #pragma unroll
         for (int j = 0; j < WARPS; ++j) a = A::max_(a, red[j][threadIdx.x]);
-        part[threadIdx.x] = a;
+        const unsigned int me = cluster.block_rank();
+        for (unsigned int r = 0; r < n_cta; ++r) cluster.map_shared_rank(&recv[0][0], r)[me * PW + threadIdx.x] = a;
     }
-    // ---- exchange partial maxima inside the cluster; one thread per column makes its scale and divisor ----
-    cluster.sync();
+    cluster.sync();  // the stores above are visible after it; nobody reads or writes a peer's memory from here on
+    // one thread per column makes its scale and divisor
     if (threadIdx.x < PW) {
+        T v[kMaxCluster];
+#pragma unroll
+        for (int r = 0; r < kMaxCluster; ++r) v[r] = ((unsigned)r < n_cta) ? recv[r][threadIdx.x] : A::lowest();
         T a = A::lowest();
-        const unsigned int n = cluster.num_blocks();
-        for (unsigned int r = 0; r < n; ++r) {
-            const T *remote = cluster.map_shared_rank(part, r);
-            a = A::max_(a, remote[threadIdx.x]);
-        }
+#pragma unroll
+        for (int r = 0; r < kMaxCluster; ++r) a = A::max_(a, v[r]);
         const T s = A::div_(a, A::qmax(QMax<Q>::value));
         div_s[threadIdx.x] = A::prepare(s);
         const int64_t c = (int64_t)blockIdx.y * PW + threadIdx.x;
         if (blockIdx.x == 0 && c < cols) scale[c] = s;
     }
-    cluster.sync();  // div_s is complete, and nobody leaves while a peer may still read its part
+    __syncthreads();
 
     // ---- phase 2: quantize ----
     if (col_ok) {
@@ -566,7 +581,7 @@ int launch_quantize_cols(const T *w, Q *wq, T *scale, int64_t rows, int64_t cols
 
     // Split the rows over the largest portable cluster that still leaves every CTA a full sweep,
     // and keep the slice in shared memory when it fits.
-    int cluster = 8;
+    int cluster = kMaxCluster;
     while (cluster > 1 && ceil_div(rows, cluster) < TY) cluster >>= 1;
     const int64_t rows_per_cta = ceil_div(rows, cluster);
     size_t tile_bytes = (size_t)rows_per_cta * PW * sizeof(T);
