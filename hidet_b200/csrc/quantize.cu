@@ -210,7 +210,14 @@ struct AbsMaxVec {
 #pragma unroll
         for (int i = 0; i < VEC; ++i) m[i] = Arith<T>::max_(m[i], Arith<T>::abs_(x.v[i]));
     }
-    __device__ __forceinline__ void result(T *out) const {
+    // The maxima over this thread's values and those of the lanes `TX`, `2 TX`, ... away in its warp (TX = 32: its own).
+    template <int TX>
+    __device__ __forceinline__ void finish(T *out) {
+#pragma unroll
+        for (int off = TX; off < 32; off <<= 1) {
+#pragma unroll
+            for (int i = 0; i < VEC; ++i) m[i] = Arith<T>::max_(m[i], __shfl_xor_sync(0xffffffffu, m[i], off));
+        }
 #pragma unroll
         for (int i = 0; i < VEC; ++i) out[i] = m[i];
     }
@@ -241,12 +248,28 @@ struct AbsMaxVec<__half, 8> {
             lo[j] = __hmin2(lo[j], x2[j]);
         }
     }
-    __device__ __forceinline__ void result(__half *out) const {
+    template <int TX>
+    __device__ __forceinline__ void finish(__half *out) {
+        const __half2 zero = __floats2half2_rn(0.0f, 0.0f);
+        const uint32_t lowest2 = 0xFBFFFBFFu;  // (-65504, -65504)
+        __half2 m[4];
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
-            const __half h[2] = {__low2half(hi[j]), __high2half(hi[j])}, l[2] = {__low2half(lo[j]), __high2half(lo[j])};
+            // per half: lo < 0 ? max(hi, -lo) : hi, written as max(hi, lo < 0 ? -lo : lowest); hi >= lowest always
+            const uint32_t below = __hlt2_mask(lo[j], zero);
+            const __half2 neg = __hneg2(lo[j]);
+            const uint32_t cand = (*reinterpret_cast<const uint32_t *>(&neg) & below) | (lowest2 & ~below);
+            m[j] = __hmax2(hi[j], *reinterpret_cast<const __half2 *>(&cand));
+        }
 #pragma unroll
-            for (int e = 0; e < 2; ++e) out[2 * j + e] = __hlt(l[e], (__half)0.0f) ? __hmax(h[e], __hneg(l[e])) : h[e];
+        for (int off = TX; off < 32; off <<= 1) {
+#pragma unroll
+            for (int j = 0; j < 4; ++j) m[j] = __hmax2(m[j], __shfl_xor_sync(0xffffffffu, m[j], off));
+        }
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            out[2 * j] = __low2half(m[j]);
+            out[2 * j + 1] = __high2half(m[j]);
         }
     }
 };
@@ -326,13 +349,7 @@ __global__ void __launch_bounds__(kThreads) quantize_cols_kernel(const T *__rest
         }
     }
     T m[VEC];
-    acc.result(m);
-    // the rows of one sweep that a warp holds: lanes tx, tx + TX, tx + 2 TX, ...
-#pragma unroll
-    for (int off = TX; off < 32; off <<= 1) {
-#pragma unroll
-        for (int i = 0; i < VEC; ++i) m[i] = A::max_(m[i], __shfl_xor_sync(0xffffffffu, m[i], off));
-    }
+    acc.template finish<TX>(m);                // over the rows of a sweep that this warp holds: lanes tx, tx + TX, ...
     if ((threadIdx.x & 31) < TX) {
 #pragma unroll
         for (int i = 0; i < VEC; ++i) red[threadIdx.x >> 5][tx * VEC + i] = m[i];
@@ -421,7 +438,7 @@ __global__ void __launch_bounds__(kThreads) quantize_rows_kernel(const T *__rest
     }
     for (int64_t i = threadIdx.x + REG_CHUNKS * stride; i < nvec; i += stride) acc.add(load_vec<T, VEC>(src + i * VEC));
     T each[VEC];
-    acc.result(each);
+    acc.template finish<32>(each);
     T m = A::lowest();
 #pragma unroll
     for (int e = 0; e < VEC; ++e) m = A::max_(m, each[e]);
