@@ -330,6 +330,31 @@ def extra_sections(torch, hidet_b200, device, stream, peaks):
     out['quantize'] = {'K': k, 'N': n, 'dtype': 'f16->i8, dims=0', 'us_per_launch': round(us, 2), 'GBps': round(qbytes / us / 1e3, 1),
                        'frac_of_hbm_peak': round(qbytes / us / 1e3 / peaks['hbm_gbs'], 4)}
     del ws
+    # quantize and dequantize over the projection shapes, both reduced dimensions
+    family = []
+    for k, n in ((4096, 4096), (4096, 11008), (11008, 4096)):
+        count = 8 if k * n < 3e7 else 4   # > L2 in rotation either way
+        ws = [(torch.randn(k, n, generator=gen, device=device, dtype=torch.float32) * 0.02).to(torch.float16) for _ in range(count)]
+        for dims in (0, -1):
+            def qfn():
+                for w in ws:
+                    hidet_b200.symmetric_quantize(w, 'int8', dims=dims)
+
+            q_us = time_graph(torch, stream, qfn, len(ws))
+            qs = [hidet_b200.symmetric_quantize(w, 'int8', dims=dims) for w in ws]
+
+            def dfn():
+                for wq, sc in qs:
+                    hidet_b200.symmetric_dequantize(wq, sc, dims=dims)
+
+            d_us = time_graph(torch, stream, dfn, len(qs))
+            del qs
+            nbytes = 3 * k * n
+            family.append({'rows': k, 'cols': n, 'dims': dims,
+                           'quantize_us': round(q_us, 2), 'quantize_frac_of_hbm_peak': round(nbytes / q_us / 1e3 / peaks['hbm_gbs'], 4),
+                           'dequantize_us': round(d_us, 2), 'dequantize_frac_of_hbm_peak': round(nbytes / d_us / 1e3 / peaks['hbm_gbs'], 4)})
+        del ws
+    out['quantize_family'] = family
     # The 70B-shaped layer of the multi-GPU runs, unsharded on this one GPU: the base of their speed-up.
     stack = make_quantized_stack(torch, hidet_b200, device, K_70B, N_70B, 2, seed=70)
     one_gpu = []
