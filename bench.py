@@ -380,7 +380,7 @@ def extra_sections(torch, hidet_b200, device, stream, peaks):
     for m, n, k in ((1, 4096, 4096), (1, 12288, 4096), (1, 4096, 12288)):
         gsize = 128
         gen = torch.Generator(device=device).manual_seed(5)
-        count = 12  # 100 to 300 MB of codes in rotation
+        count = max(12, -(-160_000_000 // (k * n // 2)))  # 160 to 300 MB of codes in rotation: larger than L2
         codes = [cast_f16_to_u4(torch.randint(0, 16, (k, n), device=device, generator=gen).to(torch.float16)) for _ in range(count)]
         scale = (torch.rand(k // gsize, n, device=device, generator=gen) * 0.01).to(torch.float16)
         zeros = (torch.rand(k // gsize, n, device=device, generator=gen) * 15).to(torch.float16)
