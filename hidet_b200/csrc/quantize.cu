@@ -473,6 +473,54 @@ __global__ void __launch_bounds__(kThreads) quantize_rows_kernel(const T *__rest
     }
 }
 
+// A warp per row, for rows of at most kWarpRowBytes: the row is brought into the warp's part of shared memory by
+// asynchronous 16-byte copies, all in flight at once, and both phases read it from there.  A lane reads back only
+// what it copied itself and the warps of a CTA share nothing, so there is no barrier; the reduction is one round
+// of warp shuffles instead of a CTA's.  grid = ceil(rows / W) CTAs of W <= kRowWarps warps (fewer for long rows, so
+// that a CTA's rows stay near kRowCtaBytes and several CTAs fit an SM).
+constexpr int kRowWarps = 4;
+constexpr size_t kWarpRowBytes = 48 * 1024;
+constexpr size_t kRowCtaBytes = 48 * 1024;
+
+template <typename T, typename Q, int VEC>
+__global__ void __launch_bounds__(kRowWarps * 32) quantize_rows_warp_kernel(const T *__restrict__ w, Q *__restrict__ wq,
+                                                                            T *__restrict__ scale, int64_t rows, int64_t cols) {
+    using A = Arith<T>;
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int64_t row = (int64_t)blockIdx.x * (blockDim.x >> 5) + warp;
+    if (row >= rows) return;
+    const int nvec = (int)(cols / VEC);       // cols % VEC == 0, and a row is at most kWarpRowBytes
+    T *mine = reinterpret_cast<T *>(smem_raw) + (size_t)warp * cols;
+    const T *src = w + row * cols;
+    Q *dst = wq + row * cols;
+
+    {
+        const uint32_t base = smem_u32(mine);
+        for (int i = lane; i < nvec; i += 32) copy_async_16(base + (uint32_t)(i * VEC * sizeof(T)), src + (size_t)i * VEC);
+        copy_async_wait_all();
+    }
+    AbsMaxVec<T, VEC> acc;
+    acc.init();
+#pragma unroll 4
+    for (int i = lane; i < nvec; i += 32) acc.add(load_vec<T, VEC>(mine + (size_t)i * VEC));
+    T each[VEC];
+    acc.template finish<32>(each);
+    T m = A::lowest();
+#pragma unroll
+    for (int e = 0; e < VEC; ++e) m = A::max_(m, each[e]);
+    m = warp_max<T>(m);
+    const T s_val = A::div_(m, A::qmax(QMax<Q>::value));
+    if (lane == 0) scale[row] = s_val;
+    const typename A::Divisor s = A::prepare(s_val);
+#pragma unroll 4
+    for (int i = lane; i < nvec; i += 32) {
+        Vec<Q, VEC> q;
+        QuantVec<T, Q, VEC, typename A::Divisor>::template run<false>(load_vec<T, VEC>(mine + (size_t)i * VEC), &s, q);
+        store_vec<Q, VEC>(dst + (size_t)i * VEC, q);
+    }
+}
+
 // ---------------------------------------------------------------------------------------------
 // dequantize: a CTA covers kDqRows rows of kDqVecs vectors; a thread keeps its column and walks the rows
 // ---------------------------------------------------------------------------------------------
@@ -630,6 +678,16 @@ int launch_quantize_cols(const T *w, Q *wq, T *scale, int64_t rows, int64_t cols
 template <typename T, typename Q, int VEC>
 int launch_quantize_rows(const T *w, Q *wq, T *scale, int64_t rows, int64_t cols, cudaStream_t stream) {
     if (rows > 2147483647LL) return set_error(B200Q_UNSUPPORTED, "symmetric_quantize: %lld rows exceed the grid limit", (long long)rows);
+    if (VEC > 1 && (size_t)cols * sizeof(T) <= kWarpRowBytes) {
+        const size_t row_bytes = (size_t)cols * sizeof(T);
+        int warps = (int)(kRowCtaBytes / row_bytes);
+        warps = warps < 1 ? 1 : (warps > kRowWarps ? kRowWarps : warps);
+        const size_t smem = warps * row_bytes;  // at most kRowCtaBytes, the default limit for dynamic shared memory
+        auto kernel = quantize_rows_warp_kernel<T, Q, VEC>;
+        kernel<<<(unsigned)ceil_div(rows, warps), warps * 32, smem, stream>>>(w, wq, scale, rows, cols);
+        B200Q_CHECK_LAUNCH("quantize_rows_warp_kernel");
+        return B200Q_OK;
+    }
     const int64_t nvec = cols / VEC;
     int threads = (int)round_up(nvec < 32 ? 32 : nvec, 32);
     if (threads > kThreads) threads = kThreads;
