@@ -599,20 +599,21 @@ bool aligned(const void *p, size_t a) { return (reinterpret_cast<uintptr_t>(p) %
 // ---------------------------------------------------------------------------------------------
 // embedding lookup in a row-quantized table: out[i, :] = T(table[idx[i], :]) * scale[idx[i]]
 // ---------------------------------------------------------------------------------------------
-// One vector of VEC values per thread, `vec_per_row` threads' worth per looked-up row.  The arithmetic is
-// that of dequantize_kernel with reduce_dim = 1, so a lookup equals the row of the dequantized table bit
-// for bit.  An index outside [0, vocab) (after adding vocab to a negative one) yields a row of zeros and
-// sets bit 30 of the device status word.
+// The tiling of dequantize_kernel over the looked-up rows: a thread keeps its column and walks kDqRows / kDqSweep
+// indices.  The arithmetic is that of dequantize_kernel with reduce_dim = 1, so a lookup equals the row of the
+// dequantized table bit for bit.  An index outside [0, vocab) (after adding vocab to a negative one) yields a row of
+// zeros and sets bit 30 of the device status word.  grid = (index blocks, column blocks)
 template <typename T, typename Q, typename I, int VEC>
 __global__ void __launch_bounds__(kThreads) embedding_dequant_kernel(const Q *__restrict__ table, const T *__restrict__ scale,
                                                                      const I *__restrict__ idx, T *__restrict__ out, int64_t vocab,
                                                                      int64_t dim, int64_t n_idx, unsigned int *status) {
-    using A = Arith<T>;
-    const int64_t vec_per_row = dim / VEC;
-    const int64_t total = n_idx * vec_per_row;
-    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
-        const int64_t r = i / vec_per_row;
-        const int64_t c = (i - r * vec_per_row) * VEC;
+    const int64_t c = ((int64_t)blockIdx.y * kDqVecs + (threadIdx.x % kDqVecs)) * VEC;
+    if (c >= dim) return;                         // dim % VEC == 0 whenever VEC > 1
+    const int64_t r0 = (int64_t)blockIdx.x * kDqRows + threadIdx.x / kDqVecs;
+#pragma unroll
+    for (int i = 0; i < kDqRows / kDqSweep; ++i) {
+        const int64_t r = r0 + i * kDqSweep;
+        if (r >= n_idx) break;
         int64_t row = (int64_t)idx[r];
         if (row < 0) row += vocab;
         Vec<T, VEC> o;
@@ -621,10 +622,8 @@ __global__ void __launch_bounds__(kThreads) embedding_dequant_kernel(const Q *__
             for (int e = 0; e < VEC; ++e) o.v[e] = (T)0.0f;
             if (c == 0 && status != nullptr) atomicOr(status, 0x40000000u);
         } else {
-            const Vec<Q, VEC> q = load_vec<Q, VEC>(table + row * dim + c);
             const T s = scale[row];
-#pragma unroll
-            for (int e = 0; e < VEC; ++e) o.v[e] = A::template dequant<Q>(q.v[e], s);
+            DequantVec<T, Q, VEC>::template run<false>(load_vec<Q, VEC>(table + row * dim + c), &s, o);
         }
         store_vec<T, VEC>(out + r * dim + c, o);
     }
@@ -744,16 +743,18 @@ int embedding_typed(const void *table_, const void *scale_, const void *idx_, vo
     T *out = static_cast<T *>(out_);
     constexpr int VEC = 16 / sizeof(T);
     const bool vec_ok = (dim % VEC == 0) && aligned(out, 16) && aligned(table, VEC * sizeof(Q));
-    const int64_t total = n_idx * (vec_ok ? dim / VEC : dim);
-    int64_t blocks = ceil_div(total, kThreads);
-    const int64_t cap = (int64_t)sm_count() * 16;
-    if (cap > 0 && blocks > cap) blocks = cap;
-    if (blocks < 1) blocks = 1;
+    if (n_idx == 0 || dim == 0) return B200Q_OK;
+    const int64_t row_blocks = ceil_div(n_idx, kDqRows);
+    const int64_t col_blocks = ceil_div(vec_ok ? dim / VEC : dim, kDqVecs);
+    if (row_blocks > 2147483647LL || col_blocks > 65535) {
+        return set_error(B200Q_UNSUPPORTED, "embedding_dequantize: %lld indices of %lld values exceed the grid limit", (long long)n_idx, (long long)dim);
+    }
+    const dim3 grid((unsigned)row_blocks, (unsigned)col_blocks, 1);
     unsigned int *status = device_status_word();
     if (vec_ok) {
-        embedding_dequant_kernel<T, Q, I, VEC><<<(unsigned)blocks, kThreads, 0, stream>>>(table, scale, idx, out, vocab, dim, n_idx, status);
+        embedding_dequant_kernel<T, Q, I, VEC><<<grid, kThreads, 0, stream>>>(table, scale, idx, out, vocab, dim, n_idx, status);
     } else {
-        embedding_dequant_kernel<T, Q, I, 1><<<(unsigned)blocks, kThreads, 0, stream>>>(table, scale, idx, out, vocab, dim, n_idx, status);
+        embedding_dequant_kernel<T, Q, I, 1><<<grid, kThreads, 0, stream>>>(table, scale, idx, out, vocab, dim, n_idx, status);
     }
     B200Q_CHECK_LAUNCH("embedding_dequant_kernel");
     return B200Q_OK;
